@@ -1,0 +1,117 @@
+// Internal declarations shared by the translation units of libhpspmm.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "hpspmm.h"
+
+// Context: device ordinal, cached device properties, grow-only scratch and the text
+// of the last CUDA error.  Takes the place of starml's allocator and handle
+// registries (spmm/starml/basic/allocator.cpp:21-48, spmm/starml/basic/handle.cpp:11-17).
+struct hpspmm_ctx {
+  int device;
+  int sm_count;
+  int64_t l2_bytes;
+  int max_smem_optin;
+  int64_t launches;
+  // scratch for plan-less calls: chunk table and carries
+  void* scratch;
+  size_t scratch_bytes;
+  // staging for the host-buffer entry point
+  void* stage;
+  size_t stage_bytes;
+  int* flag;  // one device int used by validation and plan building
+  char err[256];
+};
+
+// Chunk table of one sparsity structure.
+//   chunk_start[c]  first nnz of chunk c (n_chunks + 1 entries)
+//   chunk_row[c]    row holding nnz chunk_start[c]
+//   carry_row[c]    row whose partial sum chunk c hands on, or -1
+//   carry_val[c*K..] that partial sum
+struct hpspmm_plan {
+  int device;
+  int64_t M, nnz;
+  int32_t chunk_nnz;
+  int64_t n_chunks;
+  int64_t n_split_chunks;  // chunks that end inside a row
+  int64_t max_K;
+  int32_t* chunk_start;
+  int32_t* chunk_row;
+  int32_t* carry_row;
+  float* carry_val;
+  size_t bytes;
+};
+
+static inline int hpspmm_set_err(hpspmm_ctx* ctx, int status, const char* what, cudaError_t e) {
+  if (ctx) snprintf(ctx->err, sizeof(ctx->err), "%s: %s", what, cudaGetErrorString(e));
+  return status;
+}
+
+#define HPSPMM_CUDA_TRY(ctx, call)                                               \
+  do {                                                                           \
+    cudaError_t e__ = (call);                                                    \
+    if (e__ != cudaSuccess)                                                      \
+      return hpspmm_set_err((ctx), e__ == cudaErrorMemoryAllocation ? HPSPMM_ERR_OOM \
+                                                                   : HPSPMM_ERR_CUDA, \
+                            #call, e__);                                         \
+  } while (0)
+
+#define HPSPMM_REQUIRE(ctx, cond, msg)                                     \
+  do {                                                                     \
+    if (!(cond)) {                                                         \
+      if (ctx) snprintf((ctx)->err, sizeof((ctx)->err), "invalid argument: %s", msg); \
+      return HPSPMM_ERR_INVALID;                                           \
+    }                                                                      \
+  } while (0)
+
+// Makes the context's device current for the calling thread for the duration of a call.
+struct hpspmm_device_guard {
+  int prev;
+  bool switched;
+  explicit hpspmm_device_guard(int dev) : prev(-1), switched(false) {
+    if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) {
+      cudaSetDevice(dev);
+      switched = true;
+    }
+  }
+  ~hpspmm_device_guard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+int hpspmm_ensure_scratch(hpspmm_ctx* ctx, size_t bytes);
+int hpspmm_ensure_stage(hpspmm_ctx* ctx, size_t bytes);
+
+// nominal chunk size for a dense width
+int32_t hpspmm_default_chunk_nnz(int64_t K);
+
+// Builds chunk_start / chunk_row for (M, nnz, row_ptr) into the given arrays (device).
+// split_count (device int, may be null) receives the number of chunks ending mid-row.
+int hpspmm_launch_chunk_table(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
+                              int32_t chunk_nnz, int64_t n_chunks, int32_t* chunk_start,
+                              int32_t* chunk_row, int* split_count, cudaStream_t stream);
+
+// ---- counter-based PRNG shared by host and device --------------------------------------
+// splitmix64 finaliser over (seed, stream, index); 24 high bits -> [0, 1).
+#if defined(__CUDACC__)
+#define HPSPMM_HD __host__ __device__ __forceinline__
+#else
+#define HPSPMM_HD static inline
+#endif
+
+HPSPMM_HD uint64_t hpspmm_mix64(uint64_t z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+HPSPMM_HD uint64_t hpspmm_rand64(uint64_t seed, uint64_t stream, uint64_t index) {
+  uint64_t k = hpspmm_mix64(seed * 0x9E3779B97F4A7C15ull + stream + 0x632BE59BD9B4E019ull);
+  return hpspmm_mix64(k + index * 0x9E3779B97F4A7C15ull);
+}
+
+// u in [0,1) on a 2^-24 grid: exact in fp32, so host and device agree bit for bit.
+HPSPMM_HD float hpspmm_u01(uint64_t bits) { return (float)(uint32_t)(bits >> 40) * (1.0f / 16777216.0f); }

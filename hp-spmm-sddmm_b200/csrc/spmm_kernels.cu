@@ -1,0 +1,805 @@
+// FP32 CSR SpMM for sm_100a: C = A * B with A in CSR, B and C dense row-major.
+//
+// Replaces the reference's GESpMM / LBSpMM kernel set (spmm/mm/spmm_kernel.cu:247-477).
+// Scheduling: the nnz axis is cut into chunks of a nominal size S.  A cut that falls
+// inside a row no longer than S is moved back to the start of that row, so short rows
+// stay whole; a cut inside a longer ("heavy") row stays where it is, so heavy rows are
+// split across chunks (a merge-path split restricted to heavy rows).  One sub-warp of
+// W = K/4 lanes (a "worker") owns one chunk; each lane owns four adjacent columns and
+// reads / writes them as one float4.  The worker loads W (col, val) pairs with one
+// coalesced load per lane, broadcasts them with sub-warp shuffles, and issues the
+// gathers of B in batches of U independent 16-byte loads per lane.
+// A row that ends inside a chunk is stored once, by plain stores.  A chunk that ends
+// inside a heavy row hands its partial sum on through a carry slot; a second, tiny
+// kernel adds the carries of each split row, in chunk order, to the row the owner
+// stored -- so results are bit-reproducible from run to run (no atomics on this path).
+// Empty rows are zeroed by extra blocks at the end of the same grid.
+#include <new>
+
+#include "device_utils.cuh"
+#include "hpspmm_internal.h"
+
+namespace {
+
+using namespace hpspmm;
+
+constexpr int kBlockThreads = 256;
+
+// ---- chunk table -----------------------------------------------------------------------
+
+__global__ void chunk_table_kernel(int M, int nnz, const int* __restrict__ row_ptr, int S,
+                                   int n_chunks, int* __restrict__ chunk_start,
+                                   int* __restrict__ chunk_row, int* __restrict__ split_count) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c > n_chunks) return;
+  if (c == n_chunks) {
+    chunk_start[c] = nnz;
+    return;
+  }
+  const int t = c * S;
+  // first index i in [0, M] with row_ptr[i] > t
+  int lo = 0, hi = M + 1;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(row_ptr + mid) <= t)
+      lo = mid + 1;
+    else
+      hi = mid;
+  }
+  int r = lo - 1;
+  r = r < 0 ? 0 : (r > M - 1 ? M - 1 : r);  // only a malformed row_ptr can need this
+  const int rs = __ldg(row_ptr + r), re = __ldg(row_ptr + r + 1);
+  const int start = (re - rs <= S) ? rs : t;
+  chunk_start[c] = c == 0 ? 0 : start;
+  chunk_row[c] = r;
+  if (split_count != nullptr && c > 0 && start != rs) atomicAdd(split_count, 1);
+}
+
+// ---- empty rows ------------------------------------------------------------------------
+
+// Blocks past the chunk blocks walk all rows and write zeros into the empty ones.
+__device__ __forceinline__ void zero_empty_rows(int M, int K, const int* __restrict__ row_ptr,
+                                                float* __restrict__ C, int zero_block,
+                                                int n_zero_blocks) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps_per_block = kBlockThreads / 32;
+  const int64_t stride = (int64_t)n_zero_blocks * warps_per_block * 32;
+  for (int64_t r0 = ((int64_t)zero_block * warps_per_block + warp) * 32; r0 < M; r0 += stride) {
+    const int64_t r = r0 + lane;
+    bool empty = false;
+    if (r < M) empty = __ldg(row_ptr + r) == __ldg(row_ptr + r + 1);
+    unsigned m = __ballot_sync(0xffffffffu, empty);
+    while (m) {
+      const int b = __ffs(m) - 1;
+      m &= m - 1;
+      float* crow = C + (r0 + b) * (int64_t)K;
+      if ((K & 3) == 0) {
+        for (int c = lane * 4; c < K; c += 128) st_stream(crow + c, make_float4(0.f, 0.f, 0.f, 0.f));
+      } else {
+        for (int c = lane; c < K; c += 32) crow[c] = 0.f;
+      }
+    }
+  }
+}
+
+// Next non-empty row after `row`, given that entry j (< nnz) follows the end of `row`.
+__device__ __forceinline__ void advance_row(const int* __restrict__ row_ptr, int M, int j,
+                                            int& row, int& row_end) {
+  ++row;
+  int e = __ldg(row_ptr + row + 1);
+  int probes = 0;
+  while (e == j) {
+    if (++probes == 8) {
+      // a long run of empty rows: finish with a binary search for the row holding j
+      int lo = row + 1, hi = M + 1;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(row_ptr + mid) <= j)
+          lo = mid + 1;
+        else
+          hi = mid;
+      }
+      row = lo - 1;
+      e = __ldg(row_ptr + row + 1);
+      break;
+    }
+    ++row;
+    e = __ldg(row_ptr + row + 1);
+  }
+  row_end = e;
+}
+
+// ---- specialised kernel: K = 4 * W * R -------------------------------------------------
+
+template <int W, int R, int U, bool HINT, bool ROWSPLIT>
+__global__ void __launch_bounds__(kBlockThreads)
+spmm_balanced_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict__ row_ptr,
+                     const int* __restrict__ col_idx, const float* __restrict__ vals,
+                     const float* __restrict__ B, float* __restrict__ C,
+                     const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
+                     int* __restrict__ carry_row, float* __restrict__ carry_val) {
+  constexpr int K = 4 * W * R;
+  if ((int)blockIdx.x >= n_chunk_blocks) {
+    zero_empty_rows(M, K, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks);
+    return;
+  }
+  const int lane = threadIdx.x & (W - 1);
+  const int worker = (int)(((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) / W);
+  if (worker >= n_chunks) return;
+  const unsigned mask = subwarp_mask<W>();
+  const uint64_t policy = policy_evict_last();
+
+  int n0, n1, row, row_end;
+  if (ROWSPLIT) {
+    row = worker;
+    n0 = __ldg(row_ptr + row);
+    n1 = __ldg(row_ptr + row + 1);
+    row_end = n1;
+  } else {
+    n0 = __ldg(chunk_start + worker);
+    n1 = __ldg(chunk_start + worker + 1);
+    row = __ldg(chunk_row + worker);
+    row_end = __ldg(row_ptr + row + 1);
+  }
+
+  float4 acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* Bl = B + lane * 4;
+
+  auto flush_row = [&](int j) {
+    float* crow = C + (int64_t)row * K + lane * 4;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      st_stream(crow + r * W * 4, acc[r]);
+      acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    advance_row(row_ptr, M, j, row, row_end);
+  };
+
+  for (int base = n0; base < n1; base += W) {
+    const int jj = base + lane;
+    int mycol = 0;
+    float myval = 0.f;
+    if (jj < n1) {
+      mycol = ld_stream(col_idx + jj);
+      myval = ld_stream(vals + jj);
+    }
+#pragma unroll 1
+    for (int u0 = 0; u0 < W; u0 += U) {
+      const int j0 = base + u0;
+      if (j0 >= n1) break;
+      if (j0 + U <= n1) {
+        float4 b[U][R];
+        float v[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+          const int c = __shfl_sync(mask, mycol, u0 + i, W);
+          v[i] = __shfl_sync(mask, myval, u0 + i, W);
+          const float* p = Bl + (int64_t)c * K;
+#pragma unroll
+          for (int r = 0; r < R; ++r) b[i][r] = ld_gather<HINT>(p + r * W * 4, policy);
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+          if (!ROWSPLIT && j0 + i == row_end) flush_row(j0 + i);
+#pragma unroll
+          for (int r = 0; r < R; ++r) fma4(acc[r], v[i], b[i][r]);
+        }
+      } else {
+        for (int i = 0; j0 + i < n1; ++i) {
+          const int c = __shfl_sync(mask, mycol, u0 + i, W);
+          const float vv = __shfl_sync(mask, myval, u0 + i, W);
+          const float* p = Bl + (int64_t)c * K;
+          float4 bb[R];
+#pragma unroll
+          for (int r = 0; r < R; ++r) bb[r] = ld_gather<HINT>(p + r * W * 4, policy);
+          if (!ROWSPLIT && j0 + i == row_end) flush_row(j0 + i);
+#pragma unroll
+          for (int r = 0; r < R; ++r) fma4(acc[r], vv, bb[r]);
+        }
+      }
+    }
+  }
+
+  if (ROWSPLIT || row_end == n1) {
+    float* crow = C + (int64_t)row * K + lane * 4;
+#pragma unroll
+    for (int r = 0; r < R; ++r) st_stream(crow + r * W * 4, acc[r]);
+    if (!ROWSPLIT && lane == 0) carry_row[worker] = -1;
+  } else {
+    float* slot = carry_val + (int64_t)worker * K + lane * 4;
+#pragma unroll
+    for (int r = 0; r < R; ++r) *reinterpret_cast<float4*>(slot + r * W * 4) = acc[r];
+    if (lane == 0) carry_row[worker] = row;
+  }
+}
+
+// ---- generic kernel: any K -------------------------------------------------------------
+// One warp per chunk; lane l owns columns kb + (s*32 + l)*VEC .. +VEC-1 for s < NS, where
+// kb = blockIdx.y * (32*VEC*NS).  VEC = 4 needs K % 4 == 0.
+template <int VEC, int NS, bool ROWSPLIT>
+__global__ void __launch_bounds__(kBlockThreads)
+spmm_generic_kernel(int M, int K, int n_chunks, int n_chunk_blocks, const int* __restrict__ row_ptr,
+                    const int* __restrict__ col_idx, const float* __restrict__ vals,
+                    const float* __restrict__ B, float* __restrict__ C,
+                    const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
+                    int* __restrict__ carry_row, float* __restrict__ carry_val) {
+  if ((int)blockIdx.x >= n_chunk_blocks) {
+    if (blockIdx.y == 0)
+      zero_empty_rows(M, K, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks);
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  const int worker = (int)(((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) >> 5);
+  if (worker >= n_chunks) return;
+  const int kb = blockIdx.y * (32 * VEC * NS);
+
+  int n0, n1, row, row_end;
+  if (ROWSPLIT) {
+    row = worker;
+    n0 = __ldg(row_ptr + row);
+    n1 = __ldg(row_ptr + row + 1);
+    row_end = n1;
+  } else {
+    n0 = __ldg(chunk_start + worker);
+    n1 = __ldg(chunk_start + worker + 1);
+    row = __ldg(chunk_row + worker);
+    row_end = __ldg(row_ptr + row + 1);
+  }
+
+  float acc[NS][VEC];
+  int colbase[NS];
+  bool live[NS];
+#pragma unroll
+  for (int s = 0; s < NS; ++s) {
+    colbase[s] = kb + (s * 32 + lane) * VEC;
+    live[s] = colbase[s] < K;  // VEC == 4 implies K % 4 == 0, so the whole vector is inside
+#pragma unroll
+    for (int x = 0; x < VEC; ++x) acc[s][x] = 0.f;
+  }
+
+  auto store_acc = [&](float* dst) {
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      if (!live[s]) continue;
+      if (VEC == 4) {
+        *reinterpret_cast<float4*>(dst + colbase[s]) =
+            make_float4(acc[s][0], acc[s][1], acc[s][2], acc[s][3]);
+      } else {
+#pragma unroll
+        for (int x = 0; x < VEC; ++x) dst[colbase[s] + x] = acc[s][x];
+      }
+    }
+  };
+
+  for (int base = n0; base < n1; base += 32) {
+    const int jj = base + lane;
+    int mycol = 0;
+    float myval = 0.f;
+    if (jj < n1) {
+      mycol = ld_stream(col_idx + jj);
+      myval = ld_stream(vals + jj);
+    }
+    const int cnt = min(32, n1 - base);
+    for (int i = 0; i < cnt; ++i) {
+      const int c = __shfl_sync(0xffffffffu, mycol, i);
+      const float v = __shfl_sync(0xffffffffu, myval, i);
+      const float* brow = B + (int64_t)c * K;
+      float bv[NS][VEC];
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        if (live[s]) {
+          if (VEC == 4) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(brow + colbase[s]));
+            bv[s][0] = t.x;
+            bv[s][1] = t.y;
+            bv[s][2] = t.z;
+            bv[s][3] = t.w;
+          } else {
+#pragma unroll
+            for (int x = 0; x < VEC; ++x) bv[s][x] = __ldg(brow + colbase[s] + x);
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) bv[s][x] = 0.f;
+        }
+      }
+      if (!ROWSPLIT && base + i == row_end) {
+        store_acc(C + (int64_t)row * K);
+#pragma unroll
+        for (int s = 0; s < NS; ++s)
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) acc[s][x] = 0.f;
+        advance_row(row_ptr, M, base + i, row, row_end);
+      }
+#pragma unroll
+      for (int s = 0; s < NS; ++s)
+#pragma unroll
+        for (int x = 0; x < VEC; ++x) acc[s][x] = fmaf(v, bv[s][x], acc[s][x]);
+    }
+  }
+
+  if (ROWSPLIT || row_end == n1) {
+    store_acc(C + (int64_t)row * K);
+    if (!ROWSPLIT && lane == 0 && blockIdx.y == 0) carry_row[worker] = -1;
+  } else {
+    store_acc(carry_val + (int64_t)worker * K);
+    if (lane == 0 && blockIdx.y == 0) carry_row[worker] = row;
+  }
+}
+
+// ---- carries ---------------------------------------------------------------------------
+// One lane per chunk finds the first carry of each split row; the warp then sums that
+// row's carries in chunk order and adds them to the stored row.
+__global__ void __launch_bounds__(kBlockThreads)
+carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
+                   const float* __restrict__ carry_val, float* __restrict__ C) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) >> 5;
+  const int64_t c0 = warp * 32;
+  if (c0 >= n_chunks) return;
+  const int64_t c = c0 + lane;
+  const int row = c < n_chunks ? carry_row[c] : -1;
+  const int prev = (c > 0 && c < n_chunks) ? carry_row[c - 1] : -1;
+  unsigned m = __ballot_sync(0xffffffffu, row >= 0 && row != prev);
+  while (m) {
+    const int b = __ffs(m) - 1;
+    m &= m - 1;
+    const int hr = __shfl_sync(0xffffffffu, row, b);
+    const int64_t first = c0 + b;
+    float* crow = C + (int64_t)hr * K;
+    if ((K & 3) == 0) {
+      for (int col = lane * 4; col < K; col += 128) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int64_t c2 = first; c2 < n_chunks && carry_row[c2] == hr; ++c2) {
+          const float4 t = *reinterpret_cast<const float4*>(carry_val + c2 * K + col);
+          s.x += t.x;
+          s.y += t.y;
+          s.z += t.z;
+          s.w += t.w;
+        }
+        float4 o = *reinterpret_cast<float4*>(crow + col);
+        o.x += s.x;
+        o.y += s.y;
+        o.z += s.z;
+        o.w += s.w;
+        *reinterpret_cast<float4*>(crow + col) = o;
+      }
+    } else {
+      for (int col = lane; col < K; col += 32) {
+        float s = 0.f;
+        for (int64_t c2 = first; c2 < n_chunks && carry_row[c2] == hr; ++c2)
+          s += carry_val[c2 * K + col];
+        crow[col] += s;
+      }
+    }
+  }
+}
+
+// ---- COO, accumulate -------------------------------------------------------------------
+// C += A * B from (row, col, val) triples in any order; zero-valued padding is skipped.
+// One warp per run of S entries; a lane owns columns (s*32 + lane)*VEC of a 128*VEC-wide
+// column block.  Partial sums leave through vector reductions on every row change.
+template <int VEC, int NS>
+__global__ void __launch_bounds__(kBlockThreads)
+spmm_coo_kernel(int K, int64_t nnz, int S, const int* __restrict__ row_idx,
+                const int* __restrict__ col_idx, const float* __restrict__ vals,
+                const float* __restrict__ B, float* __restrict__ C) {
+  const int lane = threadIdx.x & 31;
+  const int64_t worker = ((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) >> 5;
+  const int64_t n0 = worker * S;
+  if (n0 >= nnz) return;
+  const int64_t n1 = min(nnz, n0 + S);
+  const int kb = blockIdx.y * (32 * VEC * NS);
+
+  float acc[NS][VEC];
+  int colbase[NS];
+  bool live[NS];
+#pragma unroll
+  for (int s = 0; s < NS; ++s) {
+    colbase[s] = kb + (s * 32 + lane) * VEC;
+    live[s] = colbase[s] < K;
+#pragma unroll
+    for (int x = 0; x < VEC; ++x) acc[s][x] = 0.f;
+  }
+  int cur_row = -1;
+  bool dirty = false;
+
+  auto flush = [&]() {
+    if (!dirty) return;
+    float* crow = C + (int64_t)cur_row * K;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      if (live[s]) {
+        if (VEC == 4) {
+          red_add_v4(crow + colbase[s], make_float4(acc[s][0], acc[s][1], acc[s][2], acc[s][3]));
+        } else {
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) atomicAdd(crow + colbase[s] + x, acc[s][x]);
+        }
+      }
+#pragma unroll
+      for (int x = 0; x < VEC; ++x) acc[s][x] = 0.f;
+    }
+    dirty = false;
+  };
+
+  for (int64_t base = n0; base < n1; base += 32) {
+    const int64_t jj = base + lane;
+    int myrow = 0, mycol = 0;
+    float myval = 0.f;
+    if (jj < n1) {
+      myrow = ld_stream(row_idx + jj);
+      mycol = ld_stream(col_idx + jj);
+      myval = ld_stream(vals + jj);
+    }
+    const int cnt = (int)min((int64_t)32, n1 - base);
+    for (int i = 0; i < cnt; ++i) {
+      const int r = __shfl_sync(0xffffffffu, myrow, i);
+      const int c = __shfl_sync(0xffffffffu, mycol, i);
+      const float v = __shfl_sync(0xffffffffu, myval, i);
+      if (v == 0.f) continue;  // padding (and explicit zeros) contribute nothing
+      if (r != cur_row) {
+        flush();
+        cur_row = r;
+      }
+      const float* brow = B + (int64_t)c * K;
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        if (!live[s]) continue;
+        if (VEC == 4) {
+          const float4 t = __ldg(reinterpret_cast<const float4*>(brow + colbase[s]));
+          acc[s][0] = fmaf(v, t.x, acc[s][0]);
+          acc[s][1] = fmaf(v, t.y, acc[s][1]);
+          acc[s][2] = fmaf(v, t.z, acc[s][2]);
+          acc[s][3] = fmaf(v, t.w, acc[s][3]);
+        } else {
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) acc[s][x] = fmaf(v, __ldg(brow + colbase[s] + x), acc[s][x]);
+        }
+      }
+      dirty = true;
+    }
+  }
+  flush();
+}
+
+template <int W, int R, int U>
+int launch_balanced(hpspmm_ctx* ctx, bool hint, bool rowsplit, int M, int n_chunks,
+                    const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
+                    const float* B, float* C, const int32_t* chunk_start, const int32_t* chunk_row,
+                    int32_t* carry_row, float* carry_val, cudaStream_t stream) {
+  const int workers_per_block = kBlockThreads / W;
+  const int n_chunk_blocks = (n_chunks + workers_per_block - 1) / workers_per_block;
+  int n_zero_blocks = 0;
+  if (!rowsplit) {
+    n_zero_blocks = (M + kBlockThreads - 1) / kBlockThreads;
+    const int cap = ctx->sm_count * 2;
+    if (n_zero_blocks > cap) n_zero_blocks = cap;
+  }
+  const unsigned grid = (unsigned)(n_chunk_blocks + n_zero_blocks);
+  if (grid == 0) return HPSPMM_OK;
+#define HPSPMM_LAUNCH(H, RS)                                                                   \
+  spmm_balanced_kernel<W, R, U, H, RS><<<grid, kBlockThreads, 0, stream>>>(                    \
+      M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,       \
+      carry_row, carry_val)
+  if (rowsplit) {
+    if (hint) HPSPMM_LAUNCH(true, true); else HPSPMM_LAUNCH(false, true);
+  } else {
+    if (hint) HPSPMM_LAUNCH(true, false); else HPSPMM_LAUNCH(false, false);
+  }
+#undef HPSPMM_LAUNCH
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+template <int VEC>
+int launch_generic(hpspmm_ctx* ctx, bool rowsplit, int M, int K, int n_chunks,
+                   const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
+                   const float* B, float* C, const int32_t* chunk_start, const int32_t* chunk_row,
+                   int32_t* carry_row, float* carry_val, cudaStream_t stream) {
+  constexpr int NS = 4;
+  const int kblock = 32 * VEC * NS;
+  const int n_kblocks = (K + kblock - 1) / kblock;
+  const int n_chunk_blocks = (n_chunks + kBlockThreads / 32 - 1) / (kBlockThreads / 32);
+  int n_zero_blocks = 0;
+  if (!rowsplit) {
+    n_zero_blocks = (M + kBlockThreads - 1) / kBlockThreads;
+    const int cap = ctx->sm_count * 2;
+    if (n_zero_blocks > cap) n_zero_blocks = cap;
+  }
+  const dim3 grid((unsigned)(n_chunk_blocks + n_zero_blocks), (unsigned)n_kblocks, 1);
+  if (grid.x == 0) return HPSPMM_OK;
+  if (n_kblocks > 65535) return HPSPMM_ERR_UNSUPPORTED;
+  if (rowsplit)
+    spmm_generic_kernel<VEC, NS, true><<<grid, kBlockThreads, 0, stream>>>(
+        M, K, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
+        carry_row, carry_val);
+  else
+    spmm_generic_kernel<VEC, NS, false><<<grid, kBlockThreads, 0, stream>>>(
+        M, K, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
+        carry_row, carry_val);
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+int32_t hpspmm_default_chunk_nnz(int64_t K) {
+  if (K <= 32) return 128;
+  if (K <= 64) return 128;
+  return 256;
+}
+
+int hpspmm_launch_chunk_table(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
+                              int32_t chunk_nnz, int64_t n_chunks, int32_t* chunk_start,
+                              int32_t* chunk_row, int* split_count, cudaStream_t stream) {
+  const unsigned blocks = (unsigned)((n_chunks + 1 + 255) / 256);
+  chunk_table_kernel<<<blocks, 256, 0, stream>>>((int)M, (int)nnz, row_ptr, chunk_nnz,
+                                                 (int)n_chunks, chunk_start, chunk_row, split_count);
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+namespace {
+
+int check_spmm_args(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz,
+                    const void* row_ptr, const void* col_idx, const void* vals, const void* B,
+                    const void* C) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "negative size");
+  HPSPMM_REQUIRE(ctx, K >= 1, "K must be >= 1");
+  if (M > 2147483646ll || N > 2147483647ll || nnz > 2147483647ll || K > (1 << 20)) {
+    snprintf(ctx->err, sizeof(ctx->err), "sizes beyond 32-bit CSR indices");
+    return HPSPMM_ERR_UNSUPPORTED;
+  }
+  HPSPMM_REQUIRE(ctx, row_ptr != nullptr, "null row_ptr");
+  HPSPMM_REQUIRE(ctx, nnz == 0 || (col_idx && vals && B), "null operand");
+  HPSPMM_REQUIRE(ctx, M == 0 || C != nullptr, "null output");
+  if ((K & 3) == 0 && (((uintptr_t)B & 15u) || ((uintptr_t)C & 15u))) {
+    snprintf(ctx->err, sizeof(ctx->err), "dense operands must be 16-byte aligned");
+    return HPSPMM_ERR_INVALID;
+  }
+  return HPSPMM_OK;
+}
+
+int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, int64_t n_chunks,
+             const int32_t* row_ptr, const int32_t* col_idx, const float* vals, const float* B,
+             float* C, const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
+             float* carry_val, bool need_fixup, cudaStream_t stream) {
+  int st;
+  const int m = (int)M, nc = (int)n_chunks;
+  if (K == 32)
+    st = launch_balanced<8, 1, 8>(ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C,
+                                  chunk_start, chunk_row, carry_row, carry_val, stream);
+  else if (K == 64)
+    st = launch_balanced<16, 1, 8>(ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C,
+                                   chunk_start, chunk_row, carry_row, carry_val, stream);
+  else if (K == 128)
+    st = launch_balanced<32, 1, 8>(ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C,
+                                   chunk_start, chunk_row, carry_row, carry_val, stream);
+  else if ((K & 3) == 0)
+    st = launch_generic<4>(ctx, rowsplit, m, (int)K, nc, row_ptr, col_idx, vals, B, C, chunk_start,
+                           chunk_row, carry_row, carry_val, stream);
+  else
+    st = launch_generic<1>(ctx, rowsplit, m, (int)K, nc, row_ptr, col_idx, vals, B, C, chunk_start,
+                           chunk_row, carry_row, carry_val, stream);
+  if (st != HPSPMM_OK) return st;
+  if (!rowsplit && need_fixup && n_chunks > 0) {
+    const unsigned blocks = (unsigned)((n_chunks + kBlockThreads - 1) / kBlockThreads);
+    carry_fixup_kernel<<<blocks, kBlockThreads, 0, stream>>>((int)K, nc, carry_row, carry_val, C);
+    ctx->launches++;
+    HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  }
+  return HPSPMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
+                       int64_t max_K, const hpspmm_opts* opts, hpspmm_stream stream,
+                       hpspmm_plan** out) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr && out != nullptr, "null context or output");
+  *out = nullptr;
+  HPSPMM_REQUIRE(ctx, M >= 0 && nnz >= 0 && max_K >= 1, "bad size");
+  HPSPMM_REQUIRE(ctx, row_ptr != nullptr, "null row_ptr");
+  if (M > 2147483646ll || nnz > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
+  int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(max_K);
+  S = (S + 31) / 32 * 32;
+  hpspmm_device_guard guard(ctx->device);
+  hpspmm_plan* p = new (std::nothrow) hpspmm_plan();
+  if (!p) return HPSPMM_ERR_OOM;
+  memset(p, 0, sizeof(*p));
+  p->device = ctx->device;
+  p->M = M;
+  p->nnz = nnz;
+  p->chunk_nnz = S;
+  p->max_K = max_K;
+  p->n_chunks = (nnz + S - 1) / S;
+  const size_t b_start = align_up((size_t)(p->n_chunks + 1) * 4, 256);
+  const size_t b_row = align_up((size_t)(p->n_chunks + 1) * 4, 256);
+  const size_t b_crow = align_up((size_t)(p->n_chunks + 1) * 4, 256);
+  const size_t b_cval = align_up((size_t)(p->n_chunks + 1) * (size_t)max_K * 4, 256);
+  p->bytes = b_start + b_row + b_crow + b_cval;
+  char* base = nullptr;
+  cudaError_t e = cudaMalloc((void**)&base, p->bytes);
+  if (e != cudaSuccess) {
+    delete p;
+    return hpspmm_set_err(ctx, HPSPMM_ERR_OOM, "plan cudaMalloc", e);
+  }
+  p->chunk_start = (int32_t*)base;
+  p->chunk_row = (int32_t*)(base + b_start);
+  p->carry_row = (int32_t*)(base + b_start + b_row);
+  p->carry_val = (float*)(base + b_start + b_row + b_crow);
+  cudaStream_t s = (cudaStream_t)stream;
+  int st = HPSPMM_OK;
+  int split = 0;
+  e = cudaMemsetAsync(ctx->flag, 0, sizeof(int), s);
+  if (e == cudaSuccess && M > 0)
+    st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, p->n_chunks, p->chunk_start,
+                                   p->chunk_row, ctx->flag, s);
+  if (e == cudaSuccess && st == HPSPMM_OK)
+    e = cudaMemcpyAsync(&split, ctx->flag, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess && st == HPSPMM_OK) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess || st != HPSPMM_OK) {
+    cudaFree(base);
+    delete p;
+    return e != cudaSuccess ? hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "plan build", e) : st;
+  }
+  p->n_split_chunks = split;
+  *out = p;
+  return HPSPMM_OK;
+}
+
+int hpspmm_plan_destroy(hpspmm_ctx* ctx, hpspmm_plan* plan) {
+  if (!plan) return HPSPMM_OK;
+  hpspmm_device_guard guard(plan->device);
+  if (plan->chunk_start) cudaFree(plan->chunk_start);
+  delete plan;
+  (void)ctx;
+  return HPSPMM_OK;
+}
+
+int hpspmm_plan_info(const hpspmm_plan* plan, int64_t* n_chunks, int64_t* n_split_chunks,
+                     int64_t* chunk_nnz, int64_t* scratch_bytes) {
+  if (!plan) return HPSPMM_ERR_INVALID;
+  if (n_chunks) *n_chunks = plan->n_chunks;
+  if (n_split_chunks) *n_split_chunks = plan->n_split_chunks;
+  if (chunk_nnz) *chunk_nnz = plan->chunk_nnz;
+  if (scratch_bytes) *scratch_bytes = (int64_t)plan->bytes;
+  return HPSPMM_OK;
+}
+
+int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int64_t N, int64_t K,
+                        int64_t nnz, const int32_t* row_ptr, const int32_t* col_idx,
+                        const float* vals, const float* B, float* C, const hpspmm_opts* opts,
+                        hpspmm_stream stream) {
+  int st = check_spmm_args(ctx, M, N, K, nnz, row_ptr, col_idx, vals, B, C);
+  if (st != HPSPMM_OK) return st;
+  if (M == 0) return HPSPMM_OK;
+  hpspmm_device_guard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool hint = !(opts && opts->b_l2_hint == 1);
+  const int algo = opts ? opts->algo : HPSPMM_ALGO_AUTO;
+  if (algo == HPSPMM_ALGO_ROW_SPLIT) {
+    return run_spmm(ctx, hint, true, M, K, M, row_ptr, col_idx, vals, B, C, nullptr, nullptr,
+                    nullptr, nullptr, false, s);
+  }
+  HPSPMM_REQUIRE(ctx, algo == HPSPMM_ALGO_AUTO || algo == HPSPMM_ALGO_BALANCED, "unknown algo");
+  if (plan) {
+    HPSPMM_REQUIRE(ctx, plan->M == M && plan->nnz == nnz, "plan built for another matrix");
+    HPSPMM_REQUIRE(ctx, K <= plan->max_K, "K exceeds the plan's max_K");
+    HPSPMM_REQUIRE(ctx, plan->device == ctx->device, "plan built on another device");
+    return run_spmm(ctx, hint, false, M, K, plan->n_chunks, row_ptr, col_idx, vals, B, C,
+                    plan->chunk_start, plan->chunk_row, plan->carry_row, plan->carry_val,
+                    plan->n_split_chunks > 0, s);
+  }
+  int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
+  S = (S + 31) / 32 * 32;
+  const int64_t n_chunks = (nnz + S - 1) / S;
+  const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
+  const size_t b_cval = align_up((size_t)(n_chunks + 1) * (size_t)K * 4, 256);
+  st = hpspmm_ensure_scratch(ctx, 3 * b_int + b_cval);
+  if (st != HPSPMM_OK) return st;
+  char* base = (char*)ctx->scratch;
+  int32_t* chunk_start = (int32_t*)base;
+  int32_t* chunk_row = (int32_t*)(base + b_int);
+  int32_t* carry_row = (int32_t*)(base + 2 * b_int);
+  float* carry_val = (float*)(base + 3 * b_int);
+  st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, chunk_start, chunk_row,
+                                 nullptr, s);
+  if (st != HPSPMM_OK) return st;
+  return run_spmm(ctx, hint, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
+                  chunk_row, carry_row, carry_val, true, s);
+}
+
+int hpspmm_spmm_csr_f32_host(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz,
+                             const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
+                             const float* B, float* C, const hpspmm_opts* opts) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0 && K >= 1, "bad size");
+  HPSPMM_REQUIRE(ctx, row_ptr != nullptr, "null row_ptr");
+  HPSPMM_REQUIRE(ctx, nnz == 0 || (col_idx && vals && B), "null operand");
+  HPSPMM_REQUIRE(ctx, M == 0 || C != nullptr, "null output");
+  if (M == 0) return HPSPMM_OK;
+  hpspmm_device_guard guard(ctx->device);
+  const size_t b_rp = align_up((size_t)(M + 1) * 4, 256);
+  const size_t b_nz = align_up((size_t)nnz * 4, 256);
+  const size_t b_B = align_up((size_t)N * (size_t)K * 4, 256);
+  const size_t b_C = align_up((size_t)M * (size_t)K * 4, 256);
+  int st = hpspmm_ensure_stage(ctx, b_rp + 2 * b_nz + b_B + b_C);
+  if (st != HPSPMM_OK) return st;
+  char* base = (char*)ctx->stage;
+  int32_t* d_rp = (int32_t*)base;
+  int32_t* d_col = (int32_t*)(base + b_rp);
+  float* d_val = (float*)(base + b_rp + b_nz);
+  float* d_B = (float*)(base + b_rp + 2 * b_nz);
+  float* d_C = (float*)(base + b_rp + 2 * b_nz + b_B);
+  cudaStream_t s = 0;
+  HPSPMM_CUDA_TRY(ctx, cudaMemcpyAsync(d_rp, row_ptr, (size_t)(M + 1) * 4, cudaMemcpyHostToDevice, s));
+  if (nnz > 0) {
+    HPSPMM_CUDA_TRY(ctx, cudaMemcpyAsync(d_col, col_idx, (size_t)nnz * 4, cudaMemcpyHostToDevice, s));
+    HPSPMM_CUDA_TRY(ctx, cudaMemcpyAsync(d_val, vals, (size_t)nnz * 4, cudaMemcpyHostToDevice, s));
+    HPSPMM_CUDA_TRY(ctx, cudaMemcpyAsync(d_B, B, (size_t)N * (size_t)K * 4, cudaMemcpyHostToDevice, s));
+  }
+  st = hpspmm_spmm_csr_f32(ctx, nullptr, M, N, K, nnz, d_rp, d_col, d_val, d_B, d_C, opts,
+                           (hpspmm_stream)s);
+  if (st != HPSPMM_OK) return st;
+  HPSPMM_CUDA_TRY(ctx, cudaMemcpyAsync(C, d_C, (size_t)M * (size_t)K * 4, cudaMemcpyDeviceToHost, s));
+  HPSPMM_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+  return HPSPMM_OK;
+}
+
+int hpspmm_spmm_coo_f32(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz_padded,
+                        const int32_t* row_idx, const int32_t* col_idx, const float* vals,
+                        const float* B, float* C, const hpspmm_opts* opts, hpspmm_stream stream) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz_padded >= 0 && K >= 1, "bad size");
+  if (nnz_padded == 0 || M == 0) return HPSPMM_OK;
+  HPSPMM_REQUIRE(ctx, row_idx && col_idx && vals && B && C, "null operand");
+  if ((K & 3) == 0 && (((uintptr_t)B & 15u) || ((uintptr_t)C & 15u))) {
+    snprintf(ctx->err, sizeof(ctx->err), "dense operands must be 16-byte aligned");
+    return HPSPMM_ERR_INVALID;
+  }
+  hpspmm_device_guard guard(ctx->device);
+  int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : 128;
+  S = (S + 31) / 32 * 32;
+  const int64_t n_workers = (nnz_padded + S - 1) / S;
+  const int64_t blocks = (n_workers + kBlockThreads / 32 - 1) / (kBlockThreads / 32);
+  if (blocks > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  if ((K & 3) == 0) {
+    // narrow K keeps one column slab per lane so no lane idles on dead slabs
+    if (K <= 128) {
+      const dim3 grid((unsigned)blocks, 1, 1);
+      spmm_coo_kernel<4, 1><<<grid, kBlockThreads, 0, s>>>((int)K, nnz_padded, S, row_idx, col_idx,
+                                                           vals, B, C);
+    } else {
+      const int kblock = 32 * 4 * 4;
+      const dim3 grid((unsigned)blocks, (unsigned)((K + kblock - 1) / kblock), 1);
+      if (grid.y > 65535) return HPSPMM_ERR_UNSUPPORTED;
+      spmm_coo_kernel<4, 4><<<grid, kBlockThreads, 0, s>>>((int)K, nnz_padded, S, row_idx, col_idx,
+                                                           vals, B, C);
+    }
+  } else {
+    const int kblock = 32 * 4;
+    const dim3 grid((unsigned)blocks, (unsigned)((K + kblock - 1) / kblock), 1);
+    if (grid.y > 65535) return HPSPMM_ERR_UNSUPPORTED;
+    spmm_coo_kernel<1, 4><<<grid, kBlockThreads, 0, s>>>((int)K, nnz_padded, S, row_idx, col_idx,
+                                                         vals, B, C);
+  }
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+}  // extern "C"

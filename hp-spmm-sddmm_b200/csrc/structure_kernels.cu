@@ -1,0 +1,370 @@
+// Integer / structure work around the SpMM path: CSR validation, CSR -> padded COO row
+// expansion (the device form of spmm/mm/spmm_common.cpp:210-226), and a deterministic CSR
+// transpose (stable LSD radix sort of the entry positions by column index).  All outputs
+// are integer-exact and independent of thread scheduling.
+#include "hpspmm_internal.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// row holding entry j: last r with row_ptr[r] <= j
+__device__ __forceinline__ int row_of_entry(const int* __restrict__ row_ptr, int M, int j) {
+  int lo = 0, hi = M + 1;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(row_ptr + mid) <= j)
+      lo = mid + 1;
+    else
+      hi = mid;
+  }
+  const int r = lo - 1;
+  return r < 0 ? 0 : (r > M - 1 ? M - 1 : r);
+}
+
+// ---- validation ------------------------------------------------------------------------
+// bad[0] = smallest offending position + 1 (rows first, then M + 1 + entry index), 0 if none
+__global__ void validate_csr_kernel(int64_t M, int64_t N, int64_t nnz, const int* __restrict__ row_ptr,
+                                    const int* __restrict__ col_idx, unsigned long long* bad) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M + 1 + nnz; i += stride) {
+    bool ok = true;
+    if (i <= M) {
+      const int v = row_ptr[i];
+      if (i == 0) ok = v == 0;
+      if (i == M) ok = ok && v == nnz;
+      if (i > 0) ok = ok && v >= row_ptr[i - 1];
+      ok = ok && v >= 0 && v <= nnz;
+    } else {
+      const int c = col_idx[i - M - 1];
+      ok = c >= 0 && c < N;
+    }
+    if (!ok) atomicMin(bad, (unsigned long long)(i + 1));
+  }
+}
+
+// ---- CSR -> COO ------------------------------------------------------------------------
+__global__ void expand_rows_kernel(int M, int64_t nnz, int64_t padded, const int* __restrict__ row_ptr,
+                                   const int* __restrict__ col_idx, const float* __restrict__ vals,
+                                   int* __restrict__ row_out, int* __restrict__ col_out,
+                                   float* __restrict__ val_out) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < padded; j += stride) {
+    if (j < nnz) {
+      row_out[j] = row_of_entry(row_ptr, M, (int)j);
+      if (col_out) col_out[j] = col_idx[j];
+      if (val_out) val_out[j] = vals[j];
+    } else {
+      row_out[j] = 0;
+      if (col_out) col_out[j] = 0;
+      if (val_out) val_out[j] = 0.f;
+    }
+  }
+}
+
+// ---- radix sort passes -----------------------------------------------------------------
+constexpr int kItems = 16;                      // keys per thread
+constexpr int kTile = kThreads * kItems;        // keys per block
+constexpr int kWarps = kThreads / 32;
+constexpr int kWarpSpan = kTile / kWarps;       // contiguous keys per warp
+constexpr int kSteps = kWarpSpan / 32;          // == kItems
+
+// hist[d * n_tiles + tile] = number of keys of the tile with digit d
+__global__ void __launch_bounds__(kThreads)
+radix_hist_kernel(const int* __restrict__ keys, int64_t n, int shift, int n_tiles,
+                  int* __restrict__ hist) {
+  __shared__ int cnt[256];
+  cnt[threadIdx.x] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * kTile;
+  for (int i = 0; i < kItems; ++i) {
+    const int64_t idx = base + (int64_t)i * kThreads + threadIdx.x;
+    if (idx < n) atomicAdd(&cnt[(keys[idx] >> shift) & 255], 1);
+  }
+  __syncthreads();
+  hist[(int64_t)threadIdx.x * n_tiles + blockIdx.x] = cnt[threadIdx.x];
+}
+
+// Exclusive scan in three steps: per-block totals, scan of the totals by one block, rescan.
+constexpr int kScanTile = 4096;
+__global__ void __launch_bounds__(kThreads)
+scan_block_totals_kernel(const int* __restrict__ in, int64_t n, int* __restrict__ totals) {
+  __shared__ int red[kThreads];
+  const int64_t base = (int64_t)blockIdx.x * kScanTile;
+  int s = 0;
+  for (int i = threadIdx.x; i < kScanTile; i += kThreads)
+    if (base + i < n) s += in[base + i];
+  red[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = kThreads / 2; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) totals[blockIdx.x] = red[0];
+}
+
+// in-place exclusive scan of `n` ints by a single block
+__global__ void __launch_bounds__(kThreads)
+scan_single_block_kernel(int* __restrict__ data, int64_t n) {
+  __shared__ int part[kThreads];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < n; base += kThreads) {
+    const int64_t i = base + threadIdx.x;
+    const int v = i < n ? data[i] : 0;
+    part[threadIdx.x] = v;
+    __syncthreads();
+    for (int o = 1; o < kThreads; o <<= 1) {
+      const int t = (int)threadIdx.x >= o ? part[threadIdx.x - o] : 0;
+      __syncthreads();
+      part[threadIdx.x] += t;
+      __syncthreads();
+    }
+    if (i < n) data[i] = carry + part[threadIdx.x] - v;
+    __syncthreads();
+    if (threadIdx.x == kThreads - 1) carry += part[threadIdx.x];
+    __syncthreads();
+  }
+}
+
+// out[i] = totals_scanned[block] + exclusive prefix inside the block's tile; in-place safe
+__global__ void __launch_bounds__(kThreads)
+scan_rescan_kernel(int* __restrict__ data, int64_t n, const int* __restrict__ totals_scanned) {
+  __shared__ int part[kThreads];
+  constexpr int per = kScanTile / kThreads;
+  const int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * per;
+  int v[per];
+  int s = 0;
+#pragma unroll
+  for (int i = 0; i < per; ++i) {
+    v[i] = base + i < n ? data[base + i] : 0;
+    s += v[i];
+  }
+  part[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = 1; o < kThreads; o <<= 1) {
+    const int t = (int)threadIdx.x >= o ? part[threadIdx.x - o] : 0;
+    __syncthreads();
+    part[threadIdx.x] += t;
+    __syncthreads();
+  }
+  int run = totals_scanned[blockIdx.x] + part[threadIdx.x] - s;
+#pragma unroll
+  for (int i = 0; i < per; ++i) {
+    if (base + i < n) data[base + i] = run;
+    run += v[i];
+  }
+}
+
+// Stable scatter of one 8-bit digit.  Warp w of a block owns keys
+// [tile + w*kWarpSpan, tile + (w+1)*kWarpSpan) and walks them 32 at a time, so that
+// (warp, step, lane) order is ascending key position; ranks among equal digits follow it.
+// payload_in == nullptr means the payload of key i is i itself.
+// If final_* outputs are given, the pass writes the transposed matrix directly.
+__global__ void __launch_bounds__(kThreads)
+radix_scatter_kernel(const int* __restrict__ keys_in, const int* __restrict__ payload_in, int64_t n,
+                     int shift, int n_tiles, const int* __restrict__ hist_scanned,
+                     int* __restrict__ keys_out, int* __restrict__ payload_out) {
+  __shared__ int cnt[kWarps][256];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < kWarps * 256; i += kThreads) (&cnt[0][0])[i] = 0;
+  __syncthreads();
+
+  const int64_t wbase = (int64_t)blockIdx.x * kTile + (int64_t)warp * kWarpSpan;
+  int key[kSteps], pay[kSteps], rank[kSteps];
+#pragma unroll
+  for (int s = 0; s < kSteps; ++s) {
+    const int64_t idx = wbase + s * 32 + lane;
+    const bool valid = idx < n;
+    key[s] = valid ? keys_in[idx] : 0;
+    pay[s] = valid ? (payload_in ? payload_in[idx] : (int)idx) : 0;
+    const int d = (key[s] >> shift) & 255;
+    const unsigned peers = __match_any_sync(0xffffffffu, valid ? d : (0x10000 | lane));
+    const int leader = __ffs(peers) - 1;
+    int before = 0;
+    if (valid && lane == leader) {
+      before = cnt[warp][d];
+      cnt[warp][d] = before + __popc(peers);
+    }
+    before = __shfl_sync(0xffffffffu, before, leader);
+    rank[s] = before + __popc(peers & ((1u << lane) - 1u));
+    __syncwarp();
+  }
+  __syncthreads();
+  {
+    // digit threadIdx.x: turn per-warp counts into per-warp output offsets
+    const int d = threadIdx.x;
+    int run = hist_scanned[(int64_t)d * n_tiles + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const int t = cnt[w][d];
+      cnt[w][d] = run;
+      run += t;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int s = 0; s < kSteps; ++s) {
+    const int64_t idx = wbase + s * 32 + lane;
+    if (idx < n) {
+      const int d = (key[s] >> shift) & 255;
+      const int pos = cnt[warp][d] + rank[s];
+      keys_out[pos] = key[s];
+      payload_out[pos] = pay[s];
+    }
+  }
+}
+
+// row_ptr_t[c] = number of sorted keys < c
+__global__ void transposed_row_ptr_kernel(const int* __restrict__ sorted_keys, int64_t nnz, int64_t N,
+                                          int* __restrict__ row_ptr_t) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c <= N; c += stride) {
+    int64_t lo = 0, hi = nnz;
+    while (lo < hi) {
+      const int64_t mid = (lo + hi) >> 1;
+      if ((int64_t)sorted_keys[mid] < c)
+        lo = mid + 1;
+      else
+        hi = mid;
+    }
+    row_ptr_t[c] = (int)lo;
+  }
+}
+
+__global__ void transposed_gather_kernel(int M, int64_t nnz, const int* __restrict__ row_ptr,
+                                         const float* __restrict__ vals, const int* __restrict__ perm,
+                                         int* __restrict__ col_idx_t, float* __restrict__ vals_t,
+                                         int* __restrict__ perm_out) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nnz; t += stride) {
+    const int j = perm[t];
+    col_idx_t[t] = row_of_entry(row_ptr, M, j);
+    if (vals_t) vals_t[t] = vals[j];
+    if (perm_out) perm_out[t] = j;
+  }
+}
+
+unsigned grid_for(const hpspmm_ctx* ctx, int64_t n) {
+  int64_t b = (n + kThreads - 1) / kThreads;
+  const int64_t cap = (int64_t)ctx->sm_count * 32;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (unsigned)b;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hpspmm_validate_csr(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
+                        const int32_t* col_idx, int64_t* bad_pos_out, hpspmm_stream stream) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "negative size");
+  HPSPMM_REQUIRE(ctx, row_ptr != nullptr && (nnz == 0 || col_idx != nullptr), "null pointer");
+  if (bad_pos_out) *bad_pos_out = -1;
+  hpspmm_device_guard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned long long* flag = (unsigned long long*)ctx->flag;
+  HPSPMM_CUDA_TRY(ctx, cudaMemsetAsync(flag, 0xff, sizeof(unsigned long long), s));
+  validate_csr_kernel<<<grid_for(ctx, M + 1 + nnz), kThreads, 0, s>>>(M, N, nnz, row_ptr, col_idx, flag);
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  unsigned long long h = 0;
+  HPSPMM_CUDA_TRY(ctx, cudaMemcpyAsync(&h, flag, sizeof(h), cudaMemcpyDeviceToHost, s));
+  HPSPMM_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+  HPSPMM_CUDA_TRY(ctx, cudaMemsetAsync(flag, 0, sizeof(unsigned long long), s));
+  if (h != ~0ull) {
+    if (bad_pos_out) *bad_pos_out = (int64_t)h - 1;
+    snprintf(ctx->err, sizeof(ctx->err), "malformed CSR at position %lld", (long long)h - 1);
+    return HPSPMM_ERR_BAD_CSR;
+  }
+  return HPSPMM_OK;
+}
+
+int64_t hpspmm_padded_nnz(int64_t nnz, int64_t padding) {
+  if (padding <= 0 || nnz % padding == 0) return nnz;
+  return nnz + padding - nnz % padding;
+}
+
+int hpspmm_csr_to_coo_padded(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
+                             const int32_t* col_idx, const float* vals, int64_t padding,
+                             int32_t* row_out, int32_t* col_out, float* val_out,
+                             hpspmm_stream stream) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && nnz >= 0 && padding >= 0, "negative size");
+  if (M > 2147483646ll || nnz > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
+  const int64_t padded = hpspmm_padded_nnz(nnz, padding);
+  if (padded == 0) return HPSPMM_OK;
+  HPSPMM_REQUIRE(ctx, row_ptr && row_out, "null pointer");
+  HPSPMM_REQUIRE(ctx, (!col_out || col_idx) && (!val_out || vals), "missing source array");
+  hpspmm_device_guard guard(ctx->device);
+  expand_rows_kernel<<<grid_for(ctx, padded), kThreads, 0, (cudaStream_t)stream>>>(
+      (int)M, nnz, padded, row_ptr, col_idx, vals, row_out, col_out, val_out);
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+int hpspmm_csr_transpose(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
+                         const int32_t* col_idx, const float* vals, int32_t* row_ptr_t,
+                         int32_t* col_idx_t, float* vals_t, int32_t* perm_out, hpspmm_stream stream) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "negative size");
+  if (M > 2147483646ll || N > 2147483646ll || nnz > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
+  HPSPMM_REQUIRE(ctx, row_ptr && row_ptr_t, "null pointer");
+  HPSPMM_REQUIRE(ctx, nnz == 0 || (col_idx && col_idx_t), "null pointer");
+  HPSPMM_REQUIRE(ctx, !vals_t || vals, "vals_t requested without vals");
+  hpspmm_device_guard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (nnz == 0) {
+    HPSPMM_CUDA_TRY(ctx, cudaMemsetAsync(row_ptr_t, 0, (size_t)(N + 1) * 4, s));
+    return HPSPMM_OK;
+  }
+  int bits = 1;
+  while (bits < 31 && ((int64_t)1 << bits) < N) ++bits;
+  const int passes = (bits + 7) / 8;
+  const int n_tiles = (int)((nnz + kTile - 1) / kTile);
+  const int64_t hist_n = (int64_t)256 * n_tiles;
+  const int64_t scan_blocks = (hist_n + kScanTile - 1) / kScanTile;
+  const size_t b_arr = align_up((size_t)nnz * 4, 256);
+  const size_t b_hist = align_up((size_t)hist_n * 4, 256);
+  const size_t b_tot = align_up((size_t)scan_blocks * 4, 256);
+  int st = hpspmm_ensure_scratch(ctx, 4 * b_arr + b_hist + b_tot);
+  if (st != HPSPMM_OK) return st;
+  char* base = (char*)ctx->scratch;
+  int* keys[2] = {(int*)base, (int*)(base + b_arr)};
+  int* pays[2] = {(int*)(base + 2 * b_arr), (int*)(base + 3 * b_arr)};
+  int* hist = (int*)(base + 4 * b_arr);
+  int* totals = (int*)(base + 4 * b_arr + b_hist);
+
+  const int* kin = col_idx;
+  const int* pin = nullptr;
+  int cur = 0;
+  for (int p = 0; p < passes; ++p) {
+    const int shift = 8 * p;
+    radix_hist_kernel<<<n_tiles, kThreads, 0, s>>>(kin, nnz, shift, n_tiles, hist);
+    scan_block_totals_kernel<<<(unsigned)scan_blocks, kThreads, 0, s>>>(hist, hist_n, totals);
+    scan_single_block_kernel<<<1, kThreads, 0, s>>>(totals, scan_blocks);
+    scan_rescan_kernel<<<(unsigned)scan_blocks, kThreads, 0, s>>>(hist, hist_n, totals);
+    radix_scatter_kernel<<<n_tiles, kThreads, 0, s>>>(kin, pin, nnz, shift, n_tiles, hist, keys[cur],
+                                                      pays[cur]);
+    ctx->launches += 5;
+    HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+    kin = keys[cur];
+    pin = pays[cur];
+    cur ^= 1;
+  }
+  transposed_row_ptr_kernel<<<grid_for(ctx, N + 1), kThreads, 0, s>>>(kin, nnz, N, row_ptr_t);
+  transposed_gather_kernel<<<grid_for(ctx, nnz), kThreads, 0, s>>>((int)M, nnz, row_ptr, vals, pin,
+                                                                   col_idx_t, vals_t, perm_out);
+  ctx->launches += 2;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+}  // extern "C"

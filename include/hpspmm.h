@@ -1,0 +1,259 @@
+/*
+ * hpspmm.h -- C ABI of the B200 (sm_100a) FP32 CSR SpMM / SDDMM library.
+ *
+ * This is the drop-in boundary for the sparse x dense hot path of
+ * fan1997/HP-SpMM-SDDMM.  Every entry point takes plain pointers and sizes,
+ * returns an int status (0 = ok), never aborts, never throws, and -- unless
+ * stated otherwise -- only enqueues work on the caller's stream without
+ * synchronising.  Element counts and offsets are 64-bit; CSR indices are
+ * 32-bit as in the reference.  Reference citations (file:line) are paths
+ * inside the reference project.
+ *
+ * Dense operands are row-major, contiguous, leading dimension K.
+ */
+#ifndef HPSPMM_H_
+#define HPSPMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define HPSPMM_API
+#else
+#define HPSPMM_API __attribute__((visibility("default")))
+#endif
+
+typedef struct hpspmm_ctx hpspmm_ctx;   /* one per (process, device)            */
+typedef struct hpspmm_plan hpspmm_plan; /* cached nnz-balanced chunk table of A */
+typedef void* hpspmm_stream;            /* a cudaStream_t; NULL = default stream */
+typedef void* hpspmm_event;             /* a cudaEvent_t                         */
+
+/* Status codes.  Replace the reference's STARML_CHECK -> abort() behaviour
+ * (include/starml/utils/loguru.h:1526-1568) and its unchecked CUDA calls. */
+enum {
+  HPSPMM_OK = 0,
+  HPSPMM_ERR_INVALID = 1,     /* bad argument (null pointer, negative size, K <= 0 ...) */
+  HPSPMM_ERR_OOM = 2,         /* device or pinned-host allocation failed                */
+  HPSPMM_ERR_CUDA = 3,        /* a CUDA runtime call failed; see hpspmm_last_error      */
+  HPSPMM_ERR_TIMEOUT = 4,     /* a bounded device-side wait ran out                     */
+  HPSPMM_ERR_UNSUPPORTED = 5, /* size beyond what an entry point supports               */
+  HPSPMM_ERR_BAD_CSR = 6      /* CSR structure failed validation                        */
+};
+
+/* Algorithm selectors for hpspmm_opts.algo. */
+enum {
+  HPSPMM_ALGO_AUTO = 0,      /* nnz-balanced chunks, heavy rows split (the default)     */
+  HPSPMM_ALGO_BALANCED = 1,  /* same as AUTO                                            */
+  HPSPMM_ALGO_ROW_SPLIT = 2  /* one sub-warp per row; the shape of the reference's
+                                GESpMM kernels (spmm/mm/spmm_kernel.cu:247-370)          */
+};
+
+/* Runtime options; zero-initialise for defaults.  Replace the reference's
+ * in-code heuristics (spmm/mm/spmm_kernel.cu:749-750, :406-420). */
+typedef struct hpspmm_opts {
+  int32_t algo;        /* HPSPMM_ALGO_*                                              */
+  int32_t chunk_nnz;   /* nominal nnz per chunk; 0 = chosen from K; multiple of 32   */
+  int32_t b_l2_hint;   /* 0 = default (evict-last hint on B), 1 = no hint            */
+  int32_t reserved;
+} hpspmm_opts;
+
+HPSPMM_API const char* hpspmm_status_string(int status);
+HPSPMM_API const char* hpspmm_version(void);
+
+/* ---- device / memory / stream / event layer ---------------------------------
+ * Replaces starml's Allocator / Handle / copy operators:
+ * include/starml/basic/allocator.h:18-66, spmm/starml/basic/allocator_cuda.cpp:5-24,
+ * spmm/starml/basic/handle_cuda.cpp:4-23, spmm/starml/operators/cuda/copy_kernel.cu:7-41,
+ * include/spmm/utils/timer_cuda.h:6-40 (GpuTimer). */
+HPSPMM_API int hpspmm_ctx_create(int device_ordinal, hpspmm_ctx** out);
+HPSPMM_API int hpspmm_ctx_destroy(hpspmm_ctx* ctx);
+HPSPMM_API const char* hpspmm_last_error(const hpspmm_ctx* ctx);
+HPSPMM_API int hpspmm_ctx_device(const hpspmm_ctx* ctx);
+HPSPMM_API int hpspmm_ctx_sm_count(const hpspmm_ctx* ctx);
+HPSPMM_API int64_t hpspmm_ctx_l2_bytes(const hpspmm_ctx* ctx);
+/* Number of this library's kernels launched through ctx since creation. */
+HPSPMM_API int64_t hpspmm_ctx_launch_count(const hpspmm_ctx* ctx);
+
+HPSPMM_API int hpspmm_dev_alloc(hpspmm_ctx* ctx, size_t bytes, void** out);
+HPSPMM_API int hpspmm_dev_free(hpspmm_ctx* ctx, void* ptr);
+HPSPMM_API int hpspmm_host_alloc_pinned(hpspmm_ctx* ctx, size_t bytes, void** out);
+HPSPMM_API int hpspmm_host_free_pinned(hpspmm_ctx* ctx, void* ptr);
+HPSPMM_API int hpspmm_memcpy_h2d(hpspmm_ctx* ctx, void* dst, const void* src, size_t bytes,
+                                 hpspmm_stream stream);
+HPSPMM_API int hpspmm_memcpy_d2h(hpspmm_ctx* ctx, void* dst, const void* src, size_t bytes,
+                                 hpspmm_stream stream);
+HPSPMM_API int hpspmm_memcpy_d2d(hpspmm_ctx* ctx, void* dst, const void* src, size_t bytes,
+                                 hpspmm_stream stream);
+HPSPMM_API int hpspmm_memset(hpspmm_ctx* ctx, void* dst, int byte_value, size_t bytes,
+                             hpspmm_stream stream);
+HPSPMM_API int hpspmm_stream_create(hpspmm_ctx* ctx, hpspmm_stream* out);
+HPSPMM_API int hpspmm_stream_sync(hpspmm_ctx* ctx, hpspmm_stream stream);
+HPSPMM_API int hpspmm_stream_destroy(hpspmm_ctx* ctx, hpspmm_stream stream);
+HPSPMM_API int hpspmm_event_create(hpspmm_ctx* ctx, hpspmm_event* out);
+HPSPMM_API int hpspmm_event_record(hpspmm_ctx* ctx, hpspmm_event ev, hpspmm_stream stream);
+HPSPMM_API int hpspmm_event_sync(hpspmm_ctx* ctx, hpspmm_event ev);
+HPSPMM_API int hpspmm_event_elapsed_ms(hpspmm_ctx* ctx, hpspmm_event start, hpspmm_event stop,
+                                       float* ms_out);
+HPSPMM_API int hpspmm_event_destroy(hpspmm_ctx* ctx, hpspmm_event ev);
+
+/* ---- factories ---------------------------------------------------------------
+ * fill: replaces fill_matrix / fill_cuda (spmm/mm/spmm_kernel.cu:23-34) and
+ * `full` (spmm/starml/operators/cuda/factories_kernel.cu:8-17).
+ * fill_uniform: replaces `rand` (spmm/starml/operators/cpu/factories_kernel.cpp:14-28),
+ * which is unseeded in the reference; here element i of stream `stream_id` is a
+ * pure function of (seed, stream_id, i), identical on host and device. */
+HPSPMM_API int hpspmm_fill_f32(hpspmm_ctx* ctx, float* dev_ptr, int64_t count, float value,
+                               hpspmm_stream stream);
+HPSPMM_API int hpspmm_fill_uniform_f32(hpspmm_ctx* ctx, float* dev_ptr, int64_t count,
+                                       uint64_t seed, uint64_t stream_id, float lo, float hi,
+                                       hpspmm_stream stream);
+HPSPMM_API int hpspmm_host_fill_uniform_f32(float* host_ptr, int64_t count, uint64_t seed,
+                                            uint64_t stream_id, float lo, float hi);
+
+/* ---- CSR SpMM: C = A * B ---------------------------------------------------------
+ * Replaces GESpMM (include/spmm/mm/spmm_kernel.h:19, spmm/mm/spmm_kernel.cu:389-426) and
+ * the kernels it dispatches to (:247-387).  Argument order follows the reference's
+ * kernels: (m, k, row_ptr, col_idx, values, B, C), with N and nnz added.  Overwrites C;
+ * empty rows become zeros.  All pointers are device pointers.  K >= 1; K = 32/64/128
+ * take the specialised kernels, other K a generic one.
+ *
+ * plan may be NULL: the chunk table is then rebuilt into context-owned scratch on
+ * every call (one extra small kernel).  The first call that needs more scratch than
+ * the context holds allocates it (cudaMalloc, synchronising); later calls do not.
+ * Calls that share a context or a plan must not overlap on the GPU. */
+HPSPMM_API int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M,
+                                   int64_t N, int64_t K, int64_t nnz, const int32_t* row_ptr,
+                                   const int32_t* col_idx, const float* vals, const float* B,
+                                   float* C, const hpspmm_opts* opts, hpspmm_stream stream);
+
+/* Chunk table of A for repeated products with the same sparsity structure (a GNN
+ * reuses it across layers and epochs).  Reads row_ptr on the device, synchronises
+ * the stream once.  No counterpart in the reference, whose LBSpMM recomputes its
+ * grid from nnz alone (spmm/mm/spmm_kernel.cu:749-751) because its COO input
+ * carries an explicit row index per entry. */
+HPSPMM_API int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t nnz,
+                                  const int32_t* row_ptr, int64_t max_K,
+                                  const hpspmm_opts* opts, hpspmm_stream stream,
+                                  hpspmm_plan** out);
+HPSPMM_API int hpspmm_plan_destroy(hpspmm_ctx* ctx, hpspmm_plan* plan);
+/* chunks, rows split across chunks (heavy rows), nominal chunk size, scratch bytes. */
+HPSPMM_API int hpspmm_plan_info(const hpspmm_plan* plan, int64_t* n_chunks,
+                                int64_t* n_split_chunks, int64_t* chunk_nnz,
+                                int64_t* scratch_bytes);
+
+/* Same product with HOST buffers: copies A and B to the device, runs the product,
+ * copies C back, synchronises.  This is the call the end-to-end figure is timed
+ * through; it is what the reference's driver does around GESpMM
+ * (test/test_all.cpp:44-60 upload, :91-92 product) plus the download the
+ * reference only performs inside its disabled checker (spmm/utils/compare.cpp:6-7). */
+HPSPMM_API int hpspmm_spmm_csr_f32_host(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K,
+                                        int64_t nnz, const int32_t* row_ptr,
+                                        const int32_t* col_idx, const float* vals,
+                                        const float* B, float* C, const hpspmm_opts* opts);
+
+/* ---- COO SpMM: C += A * B --------------------------------------------------------
+ * Replaces LBSpMM (include/spmm/mm/spmm_kernel.h:20, spmm/mm/spmm_kernel.cu:733-768,
+ * kernel :428-477) for callers that hold the reference's padded COO arrays.  Like the
+ * reference it ACCUMULATES into C (the caller zeroes C first, test/test_all.cpp:101)
+ * and accepts padded entries (row 0, col 0, value 0); unlike the reference one call is
+ * one product (no 200 internal launches) and padded entries are skipped rather than
+ * multiplied (a NaN in B[0,:] does not leak into C[0,:]).  nnz_padded need not be a
+ * multiple of 32.  Entries of one row need not be adjacent. */
+HPSPMM_API int hpspmm_spmm_coo_f32(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K,
+                                   int64_t nnz_padded, const int32_t* row_idx,
+                                   const int32_t* col_idx, const float* vals, const float* B,
+                                   float* C, const hpspmm_opts* opts, hpspmm_stream stream);
+
+/* ---- SDDMM over the CSR pattern: out[j] = dot(X[row(j),:], Y[col[j],:]) -------------
+ * The reference ships no SDDMM (only the unused ResInfo::sddmm_* fields,
+ * include/spmm/mm/spmm_common.h:130-135).  A's values are not multiplied in. */
+HPSPMM_API int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M,
+                                    int64_t N, int64_t K, int64_t nnz, const int32_t* row_ptr,
+                                    const int32_t* col_idx, const float* X, const float* Y,
+                                    float* out_vals, const hpspmm_opts* opts,
+                                    hpspmm_stream stream);
+
+/* ---- CSR transpose on the device ---------------------------------------------------
+ * Stable counting sort by column: row_ptr_t[N+1], col_idx_t[nnz] (source rows,
+ * ascending within each transposed row), vals_t[nnz]; perm_out (optional, may be
+ * NULL) receives the source position of every transposed entry.  Deterministic.
+ * No counterpart in the reference. */
+HPSPMM_API int hpspmm_csr_transpose(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz,
+                                    const int32_t* row_ptr, const int32_t* col_idx,
+                                    const float* vals, int32_t* row_ptr_t, int32_t* col_idx_t,
+                                    float* vals_t, int32_t* perm_out, hpspmm_stream stream);
+
+/* ---- CSR -> padded COO (device) ------------------------------------------------------
+ * Replaces the host loops of get_coo_mat_from_smtx (spmm/mm/spmm_common.cpp:210-226):
+ * row_out[j] = row of entry j, then (0, 0, 0.0f) padding up to a multiple of `padding`.
+ * Output arrays hold hpspmm_padded_nnz(nnz, padding) entries. */
+HPSPMM_API int64_t hpspmm_padded_nnz(int64_t nnz, int64_t padding);
+HPSPMM_API int hpspmm_csr_to_coo_padded(hpspmm_ctx* ctx, int64_t M, int64_t nnz,
+                                        const int32_t* row_ptr, const int32_t* col_idx,
+                                        const float* vals, int64_t padding, int32_t* row_out,
+                                        int32_t* col_out, float* val_out, hpspmm_stream stream);
+
+/* ---- validation ------------------------------------------------------------------------
+ * Checks row_ptr[0] == 0, monotone row_ptr, row_ptr[M] == nnz, 0 <= col < N on the device;
+ * synchronises; returns HPSPMM_ERR_BAD_CSR and the first offending position found.
+ * The reference validates nothing (include/spmm/mm/spmm_kernel.h:17-21). */
+HPSPMM_API int hpspmm_validate_csr(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz,
+                                   const int32_t* row_ptr, const int32_t* col_idx,
+                                   int64_t* bad_pos_out, hpspmm_stream stream);
+
+/* ---- host side: seeded synthetic CSR generator --------------------------------------------
+ * Replaces the .smtx dataset loaders (spmm/mm/spmm_common.cpp:125-174) for benchmarking.
+ * Two-call protocol: hpspmm_gen_* builds the graph inside an opaque handle and reports its
+ * size; hpspmm_gen_export copies it into caller arrays; hpspmm_gen_free releases it. */
+typedef struct hpspmm_graph hpspmm_graph;
+enum { HPSPMM_VALS_ONES = 0, HPSPMM_VALS_U01 = 1, HPSPMM_VALS_UPM1 = 2 };
+/* rows with degree uniform in [deg_lo, deg_hi], distinct sorted columns */
+HPSPMM_API int hpspmm_gen_uniform_degree(int64_t M, int64_t N, int32_t deg_lo, int32_t deg_hi,
+                                         uint64_t seed, int32_t vals_kind, hpspmm_graph** out);
+/* Erdos-Renyi: Poisson(mean_degree) distinct sorted columns per row */
+HPSPMM_API int hpspmm_gen_erdos_renyi(int64_t M, int64_t N, double mean_degree, uint64_t seed,
+                                      int32_t vals_kind, hpspmm_graph** out);
+/* R-MAT: scale, edge_factor*2^scale/2 undirected draws, both directions kept,
+ * duplicates removed, self loops kept, rows sorted */
+HPSPMM_API int hpspmm_gen_rmat(int32_t scale, int32_t edge_factor, double a, double b, double c,
+                               uint64_t seed, int32_t vals_kind, hpspmm_graph** out);
+HPSPMM_API int hpspmm_gen_shape(const hpspmm_graph* g, int64_t* M, int64_t* N, int64_t* nnz);
+HPSPMM_API int hpspmm_gen_export(const hpspmm_graph* g, int32_t* row_ptr, int32_t* col_idx,
+                                 float* vals);
+HPSPMM_API int hpspmm_gen_free(hpspmm_graph* g);
+
+/* ---- host side: .smtx reader ---------------------------------------------------------------
+ * One-pass reader of the reference's text format (spmm/mm/spmm_common.cpp:125-174):
+ * line 1 "rows,cols,nnz", line 2 rows+1 offsets, line 3 nnz column ids; values are 1.0. */
+HPSPMM_API int hpspmm_read_smtx(const char* path, hpspmm_graph** out);
+
+/* ---- host side: multi-GPU row sharding ---------------------------------------------------------
+ * nnz-balanced contiguous row blocks: bounds[g] = first row r with row_ptr[r] >= g*nnz/G;
+ * bounds has G+1 entries.  Rows are never split across shards.  The reference is
+ * single-GPU; this has no counterpart there. */
+HPSPMM_API int hpspmm_shard_bounds(int64_t M, const int32_t* row_ptr_host, int32_t G,
+                                   int64_t* bounds);
+/* Local row_ptr of shard [row_lo, row_hi): local_row_ptr[i] = row_ptr[row_lo+i] - row_ptr[row_lo],
+ * row_hi-row_lo+1 entries; *nnz_lo_out / *nnz_local_out give the slice of col_idx / vals. */
+HPSPMM_API int hpspmm_shard_row_ptr(const int32_t* row_ptr_host, int64_t row_lo, int64_t row_hi,
+                                    int32_t* local_row_ptr, int64_t* nnz_lo_out,
+                                    int64_t* nnz_local_out);
+
+/* ---- host side: metric -----------------------------------------------------------------------------
+ * GFLOPS = 2*nnz*K / ms / 1e6 with the unpadded nnz (spmm/mm/spmm_common.cpp:24-31);
+ * row-length coefficient of variation (spmm/mm/spmm_common.cpp:57-67, :349-374). */
+HPSPMM_API double hpspmm_gflops(int64_t nnz, int64_t K, double ms);
+HPSPMM_API double hpspmm_row_length_cv(int64_t M, const int32_t* row_ptr_host);
+/* Compulsory bytes of one product: 4(M+1) + 8 nnz + 4 K N_ref + 4 K M. */
+HPSPMM_API double hpspmm_spmm_algorithmic_bytes(int64_t M, int64_t N_ref, int64_t K, int64_t nnz);
+HPSPMM_API double hpspmm_sddmm_algorithmic_bytes(int64_t M_ref, int64_t N_ref, int64_t K,
+                                                 int64_t M, int64_t nnz);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HPSPMM_H_ */
