@@ -49,6 +49,17 @@ __device__ __forceinline__ float ld_stream(const float* p) {
   return v;
 }
 
+// 4-byte asynchronous copy global -> shared (completion tracked per thread in commit groups).
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Streaming 16-byte store of an output row fragment.
 __device__ __forceinline__ void st_stream(float* p, float4 v) {
   asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z),

@@ -4,16 +4,21 @@
 // Scheduling: the nnz axis is cut into chunks of a nominal size S.  A cut that falls
 // inside a row no longer than S is moved back to the start of that row, so short rows
 // stay whole; a cut inside a longer ("heavy") row stays where it is, so heavy rows are
-// split across chunks (a merge-path split restricted to heavy rows).  One sub-warp of
-// W = K/4 lanes (a "worker") owns one chunk; each lane owns four adjacent columns and
-// reads / writes them as one float4.  The worker loads W (col, val) pairs with one
-// coalesced load per lane, broadcasts them with sub-warp shuffles, and issues the
-// gathers of B in batches of U independent 16-byte loads per lane.
-// A row that ends inside a chunk is stored once, by plain stores.  A chunk that ends
-// inside a heavy row hands its partial sum on through a carry slot; a second, tiny
-// kernel adds the carries of each split row, in chunk order, to the row the owner
-// stored -- so results are bit-reproducible from run to run (no atomics on this path).
-// Empty rows are zeroed by extra blocks at the end of the same grid.
+// split across chunks (a merge-path split restricted to heavy rows).  One warp owns one
+// chunk.  The warp stages (col, val) tiles of 32 entries in shared memory with
+// asynchronous copies, two tiles ahead of their use.  For K = 4*W the warp is G = 32/W
+// lane groups; in every step group g takes entry G*s+g of the tile, reads its (col, val)
+// pair as one shared-memory broadcast, and gathers its float4 of that row of B, so one
+// warp instruction gathers G rows and no two groups ever diverge (row ends are warp-
+// uniform).  Gathers are issued U steps at a time before the first FMA.  When a row
+// ends, the groups' partial sums are combined with shuffles and the row is stored once,
+// by plain stores.  A chunk that ends inside a heavy row hands its partial sum on through
+// a carry slot; a second, small kernel adds the carries of each split row, in chunk order,
+// to the row the owner stored -- so results are bit-reproducible from run to run (no
+// atomics on this path).  Empty rows are zeroed by extra blocks at the end of the same grid.
+// HPSPMM_ALGO_ROW_SPLIT keeps the reference's GESpMM shape (one sub-warp per row, every row
+// summed in storage order), which reproduces the CPU oracle bit for bit.
+#include <cstdlib>
 #include <new>
 
 #include "device_utils.cuh"
@@ -110,16 +115,31 @@ __device__ __forceinline__ void advance_row(const int* __restrict__ row_ptr, int
   row_end = e;
 }
 
-// ---- specialised kernel: K = 4 * W * R -------------------------------------------------
+// ---- sub-warp kernel: one W-lane worker per chunk or per row, K = 4 * W * R ----------------
 
-template <int W, int R, int U, bool HINT, bool ROWSPLIT>
-__global__ void __launch_bounds__(kBlockThreads)
-spmm_balanced_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict__ row_ptr,
+// Row that holds entry j, packed as (row_end << 32) | row.  Kept out of line: it runs once
+// per row, and inlining its search at every unrolled entry bloats the hot loop.  It takes
+// and returns plain integers so that the accumulators never leave registers.
+__device__ __noinline__ unsigned long long next_row_packed(const int* __restrict__ row_ptr, int M,
+                                                           int j, int row) {
+  int row_end;
+  advance_row(row_ptr, M, j, row, row_end);
+  return ((unsigned long long)(unsigned)row_end << 32) | (unsigned)row;
+}
+
+template <int W, int R, int U, int MINB, bool HINT, bool ROWSPLIT>
+__global__ void __launch_bounds__(kBlockThreads, MINB)
+spmm_subwarp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict__ row_ptr,
                      const int* __restrict__ col_idx, const float* __restrict__ vals,
                      const float* __restrict__ B, float* __restrict__ C,
                      const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
                      int* __restrict__ carry_row, float* __restrict__ carry_val) {
   constexpr int K = 4 * W * R;
+  constexpr int T = 32;       // entries per staged (col, val) tile
+  constexpr int RT = T / W;   // entries each lane stages per tile
+  constexpr int STAGES = 2;
+  __shared__ int2 tiles[kBlockThreads / W][STAGES][T];
+
   if ((int)blockIdx.x >= n_chunk_blocks) {
     zero_empty_rows(M, K, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks);
     return;
@@ -128,7 +148,8 @@ spmm_balanced_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restr
   const int worker = (int)(((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) / W);
   if (worker >= n_chunks) return;
   const unsigned mask = subwarp_mask<W>();
-  const uint64_t policy = policy_evict_last();
+  const uint64_t policy = HINT ? policy_evict_last() : 0ull;
+  int2(*my)[T] = tiles[threadIdx.x / W];
 
   int n0, n1, row, row_end;
   if (ROWSPLIT) {
@@ -143,65 +164,89 @@ spmm_balanced_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restr
     row_end = __ldg(row_ptr + row + 1);
   }
 
+  // (col, val) pairs travel global -> shared with 4-byte asynchronous copies, two tiles
+  // ahead of their use; entries past the end of the chunk are staged as (column 0, 0.0f).
+  auto stage_tile = [&](int stage, int base) {
+#pragma unroll
+    for (int t = 0; t < RT; ++t) {
+      const int e = t * W + lane;
+      const int j = base + e;
+      if (j < n1) {
+        cp_async_4(&my[stage][e].x, col_idx + j);
+        cp_async_4(&my[stage][e].y, vals + j);
+      } else {
+        my[stage][e] = make_int2(0, 0);
+      }
+    }
+    cp_async_commit();
+  };
+  stage_tile(0, n0);
+  stage_tile(1, n0 + T);
+
   float4 acc[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
   const float* Bl = B + lane * 4;
 
-  auto flush_row = [&](int j) {
-    float* crow = C + (int64_t)row * K + lane * 4;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      st_stream(crow + r * W * 4, acc[r]);
-      acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    advance_row(row_ptr, M, j, row, row_end);
-  };
-
-  for (int base = n0; base < n1; base += W) {
-    const int jj = base + lane;
-    int mycol = 0;
-    float myval = 0.f;
-    if (jj < n1) {
-      mycol = ld_stream(col_idx + jj);
-      myval = ld_stream(vals + jj);
-    }
+  int stage = 0;
+  for (int base = n0; base < n1; base += T) {
+    cp_async_wait<STAGES - 1>();
+    __syncwarp(mask);
 #pragma unroll 1
-    for (int u0 = 0; u0 < W; u0 += U) {
+    for (int u0 = 0; u0 < T; u0 += U) {
       const int j0 = base + u0;
       if (j0 >= n1) break;
-      if (j0 + U <= n1) {
-        float4 b[U][R];
-        float v[U];
+      float4 b[U][R];
+      float v[U];
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-          const int c = __shfl_sync(mask, mycol, u0 + i, W);
-          v[i] = __shfl_sync(mask, myval, u0 + i, W);
-          const float* p = Bl + (int64_t)c * K;
+      for (int i = 0; i < U; ++i) {
+        const int2 e = my[stage][u0 + i];  // same address for the whole worker: a broadcast
+        v[i] = __int_as_float(e.y);
+        const float* p = Bl + (int64_t)e.x * K;
 #pragma unroll
-          for (int r = 0; r < R; ++r) b[i][r] = ld_gather<HINT>(p + r * W * 4, policy);
-        }
+        for (int r = 0; r < R; ++r) b[i][r] = ld_gather<HINT>(p + r * W * 4, policy);
+      }
+      if (ROWSPLIT || (j0 + U <= n1 && row_end >= j0 + U)) {
+        // no row ends inside this batch: padded entries (ROWSPLIT tail) carry value 0 and
+        // are skipped below by the same test the slow path uses
+        if (!ROWSPLIT || j0 + U <= n1) {
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-          if (!ROWSPLIT && j0 + i == row_end) flush_row(j0 + i);
+          for (int i = 0; i < U; ++i)
 #pragma unroll
-          for (int r = 0; r < R; ++r) fma4(acc[r], v[i], b[i][r]);
+            for (int r = 0; r < R; ++r) fma4(acc[r], v[i], b[i][r]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < U; ++i)
+            if (j0 + i < n1)
+#pragma unroll
+              for (int r = 0; r < R; ++r) fma4(acc[r], v[i], b[i][r]);
         }
       } else {
-        for (int i = 0; j0 + i < n1; ++i) {
-          const int c = __shfl_sync(mask, mycol, u0 + i, W);
-          const float vv = __shfl_sync(mask, myval, u0 + i, W);
-          const float* p = Bl + (int64_t)c * K;
-          float4 bb[R];
 #pragma unroll
-          for (int r = 0; r < R; ++r) bb[r] = ld_gather<HINT>(p + r * W * 4, policy);
-          if (!ROWSPLIT && j0 + i == row_end) flush_row(j0 + i);
+        for (int i = 0; i < U; ++i) {
+          if (j0 + i < n1) {
+            if (j0 + i == row_end) {
+              float* crow = C + (int64_t)row * K + lane * 4;
 #pragma unroll
-          for (int r = 0; r < R; ++r) fma4(acc[r], vv, bb[r]);
+              for (int r = 0; r < R; ++r) {
+                st_stream(crow + r * W * 4, acc[r]);
+                acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+              const unsigned long long nr = next_row_packed(row_ptr, M, j0 + i, row);
+              row = (int)(unsigned)nr;
+              row_end = (int)(nr >> 32);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) fma4(acc[r], v[i], b[i][r]);
+          }
         }
       }
     }
+    __syncwarp(mask);
+    stage_tile(stage, base + STAGES * T);
+    stage ^= 1;
   }
+  cp_async_wait<0>();
 
   if (ROWSPLIT || row_end == n1) {
     float* crow = C + (int64_t)row * K + lane * 4;
@@ -213,6 +258,134 @@ spmm_balanced_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restr
 #pragma unroll
     for (int r = 0; r < R; ++r) *reinterpret_cast<float4*>(slot + r * W * 4) = acc[r];
     if (lane == 0) carry_row[worker] = row;
+  }
+}
+
+// ---- warp kernel: one warp per chunk, G = 32/W interleaved lane groups, K = 4 * W ---------
+
+template <int W>
+__device__ __forceinline__ float4 reduce_groups(float4 a) {
+  if (W <= 16) {
+    a.x += __shfl_xor_sync(0xffffffffu, a.x, 16);
+    a.y += __shfl_xor_sync(0xffffffffu, a.y, 16);
+    a.z += __shfl_xor_sync(0xffffffffu, a.z, 16);
+    a.w += __shfl_xor_sync(0xffffffffu, a.w, 16);
+  }
+  if (W <= 8) {
+    a.x += __shfl_xor_sync(0xffffffffu, a.x, 8);
+    a.y += __shfl_xor_sync(0xffffffffu, a.y, 8);
+    a.z += __shfl_xor_sync(0xffffffffu, a.z, 8);
+    a.w += __shfl_xor_sync(0xffffffffu, a.w, 8);
+  }
+  return a;
+}
+
+template <int W, int U, int MINB, bool HINT>
+__global__ void __launch_bounds__(kBlockThreads, MINB)
+spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict__ row_ptr,
+                 const int* __restrict__ col_idx, const float* __restrict__ vals,
+                 const float* __restrict__ B, float* __restrict__ C,
+                 const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
+                 int* __restrict__ carry_row, float* __restrict__ carry_val) {
+  constexpr int K = 4 * W;
+  constexpr int G = 32 / W;      // lane groups = entries gathered per warp instruction
+  constexpr int T = 32;          // entries per staged tile
+  constexpr int BATCH = U * G;   // entries per batch of gathers
+  constexpr int STAGES = 2;
+  static_assert(BATCH <= T && T % BATCH == 0, "batch must tile the staged tile");
+  __shared__ int2 tiles[kBlockThreads / 32][STAGES][T];
+
+  if ((int)blockIdx.x >= n_chunk_blocks) {
+    zero_empty_rows(M, K, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks);
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  const int g = lane / W;   // group
+  const int l = lane % W;   // position inside the group = float4 column
+  const int chunk = (int)(((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) >> 5);
+  if (chunk >= n_chunks) return;
+  const uint64_t policy = HINT ? policy_evict_last() : 0ull;
+  int2(*my)[T] = tiles[threadIdx.x >> 5];
+
+  const int n0 = __ldg(chunk_start + chunk);
+  const int n1 = __ldg(chunk_start + chunk + 1);
+  int row = __ldg(chunk_row + chunk);
+  int row_end = __ldg(row_ptr + row + 1);
+
+  auto stage_tile = [&](int stage, int base) {
+    const int j = base + lane;
+    if (j < n1) {
+      cp_async_4(&my[stage][lane].x, col_idx + j);
+      cp_async_4(&my[stage][lane].y, vals + j);
+    } else {
+      my[stage][lane] = make_int2(0, 0);   // past the chunk: column 0, value 0
+    }
+    cp_async_commit();
+  };
+  stage_tile(0, n0);
+  stage_tile(1, n0 + T);
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* Bl = B + l * 4;
+
+  // the row is complete: combine the groups' partial sums, store, start the next row
+  auto finish_row = [&](int next_entry) {
+    const float4 t = reduce_groups<W>(acc);
+    if (g == 0) st_stream(C + (int64_t)row * K + l * 4, t);
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const unsigned long long nr = next_row_packed(row_ptr, M, next_entry, row);
+    row = (int)(unsigned)nr;
+    row_end = (int)(nr >> 32);
+  };
+
+  int stage = 0;
+  for (int base = n0; base < n1; base += T) {
+    cp_async_wait<STAGES - 1>();
+    __syncwarp();
+#pragma unroll 1
+    for (int u0 = 0; u0 < T; u0 += BATCH) {
+      const int j0 = base + u0;
+      if (j0 >= n1) break;
+      float4 b[U];
+      float v[U];
+#pragma unroll
+      for (int i = 0; i < U; ++i) {
+        const int2 e = my[stage][u0 + i * G + g];   // one broadcast per group
+        v[i] = __int_as_float(e.y);
+        b[i] = ld_gather<HINT>(Bl + (int64_t)e.x * K, policy);
+      }
+      if (j0 + BATCH <= n1 && row_end >= j0 + BATCH) {
+#pragma unroll
+        for (int i = 0; i < U; ++i) fma4(acc, v[i], b[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+          const int lo = j0 + i * G;
+          const int hi = min(lo + G, n1);
+          const int mine = lo + g;
+          int cur = lo;
+          while (row_end < hi) {   // warp-uniform: the current row ends inside this step
+            if (mine >= cur && mine < row_end) fma4(acc, v[i], b[i]);
+            cur = row_end;
+            finish_row(cur);
+          }
+          if (mine >= cur && mine < hi) fma4(acc, v[i], b[i]);
+        }
+      }
+    }
+    __syncwarp();
+    stage_tile(stage, base + STAGES * T);
+    stage ^= 1;
+  }
+  cp_async_wait<0>();
+
+  const float4 t = reduce_groups<W>(acc);
+  if (row_end == n1) {
+    if (g == 0) st_stream(C + (int64_t)row * K + l * 4, t);
+    if (lane == 0) carry_row[chunk] = -1;
+  } else {
+    if (g == 0) *reinterpret_cast<float4*>(carry_val + (int64_t)chunk * K + l * 4) = t;
+    if (lane == 0) carry_row[chunk] = row;
   }
 }
 
@@ -331,8 +504,9 @@ spmm_generic_kernel(int M, int K, int n_chunks, int n_chunk_blocks, const int* _
 }
 
 // ---- carries ---------------------------------------------------------------------------
-// One lane per chunk finds the first carry of each split row; the warp then sums that
-// row's carries in chunk order and adds them to the stored row.
+// One lane per chunk finds the first carry of each split row; the warp then counts that
+// row's carries (32 at a time), sums them in chunk order with independent loads, and adds
+// the total to the row its owner stored.
 __global__ void __launch_bounds__(kBlockThreads)
 carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
                    const float* __restrict__ carry_val, float* __restrict__ C) {
@@ -345,16 +519,43 @@ carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
   const int prev = (c > 0 && c < n_chunks) ? carry_row[c - 1] : -1;
   unsigned m = __ballot_sync(0xffffffffu, row >= 0 && row != prev);
   while (m) {
-    const int b = __ffs(m) - 1;
+    const int bpos = __ffs(m) - 1;
     m &= m - 1;
-    const int hr = __shfl_sync(0xffffffffu, row, b);
-    const int64_t first = c0 + b;
+    const int hr = __shfl_sync(0xffffffffu, row, bpos);
+    const int64_t first = c0 + bpos;
+    // length of the run of carries that belong to row hr
+    int64_t len = 0;
+    for (int64_t w = first;; w += 32) {
+      const int64_t cc = w + lane;
+      const bool same = cc < n_chunks && carry_row[cc] == hr;
+      const unsigned bm = __ballot_sync(0xffffffffu, same);
+      if (bm == 0xffffffffu) {
+        len += 32;
+        continue;
+      }
+      len += __ffs(~bm) - 1;
+      break;
+    }
     float* crow = C + (int64_t)hr * K;
     if ((K & 3) == 0) {
       for (int col = lane * 4; col < K; col += 128) {
+        const float* src = carry_val + first * K + col;
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int64_t c2 = first; c2 < n_chunks && carry_row[c2] == hr; ++c2) {
-          const float4 t = *reinterpret_cast<const float4*>(carry_val + c2 * K + col);
+        int64_t i = 0;
+        for (; i + 8 <= len; i += 8) {
+          float4 t[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) t[u] = *reinterpret_cast<const float4*>(src + (i + u) * K);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            s.x += t[u].x;
+            s.y += t[u].y;
+            s.z += t[u].z;
+            s.w += t[u].w;
+          }
+        }
+        for (; i < len; ++i) {
+          const float4 t = *reinterpret_cast<const float4*>(src + i * K);
           s.x += t.x;
           s.y += t.y;
           s.z += t.z;
@@ -370,8 +571,7 @@ carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
     } else {
       for (int col = lane; col < K; col += 32) {
         float s = 0.f;
-        for (int64_t c2 = first; c2 < n_chunks && carry_row[c2] == hr; ++c2)
-          s += carry_val[c2 * K + col];
+        for (int64_t i = 0; i < len; ++i) s += carry_val[(first + i) * K + col];
         crow[col] += s;
       }
     }
@@ -466,7 +666,7 @@ spmm_coo_kernel(int K, int64_t nnz, int S, const int* __restrict__ row_idx,
   flush();
 }
 
-template <int W, int R, int U>
+template <int W, int R, int U, int MINB>
 int launch_balanced(hpspmm_ctx* ctx, bool hint, bool rowsplit, int M, int n_chunks,
                     const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
                     const float* B, float* C, const int32_t* chunk_start, const int32_t* chunk_row,
@@ -482,7 +682,7 @@ int launch_balanced(hpspmm_ctx* ctx, bool hint, bool rowsplit, int M, int n_chun
   const unsigned grid = (unsigned)(n_chunk_blocks + n_zero_blocks);
   if (grid == 0) return HPSPMM_OK;
 #define HPSPMM_LAUNCH(H, RS)                                                                   \
-  spmm_balanced_kernel<W, R, U, H, RS><<<grid, kBlockThreads, 0, stream>>>(                    \
+  spmm_subwarp_kernel<W, R, U, MINB, H, RS><<<grid, kBlockThreads, 0, stream>>>(                    \
       M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,       \
       carry_row, carry_val)
   if (rowsplit) {
@@ -491,6 +691,31 @@ int launch_balanced(hpspmm_ctx* ctx, bool hint, bool rowsplit, int M, int n_chun
     if (hint) HPSPMM_LAUNCH(true, false); else HPSPMM_LAUNCH(false, false);
   }
 #undef HPSPMM_LAUNCH
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+template <int W, int U, int MINB>
+int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* row_ptr,
+                const int32_t* col_idx, const float* vals, const float* B, float* C,
+                const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
+                float* carry_val, cudaStream_t stream) {
+  const int chunks_per_block = kBlockThreads / 32;
+  const int n_chunk_blocks = (n_chunks + chunks_per_block - 1) / chunks_per_block;
+  int n_zero_blocks = (M + kBlockThreads - 1) / kBlockThreads;
+  const int cap = ctx->sm_count * 2;
+  if (n_zero_blocks > cap) n_zero_blocks = cap;
+  const unsigned grid = (unsigned)(n_chunk_blocks + n_zero_blocks);
+  if (grid == 0) return HPSPMM_OK;
+  if (hint)
+    spmm_warp_kernel<W, U, MINB, true><<<grid, kBlockThreads, 0, stream>>>(
+        M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
+        carry_row, carry_val);
+  else
+    spmm_warp_kernel<W, U, MINB, false><<<grid, kBlockThreads, 0, stream>>>(
+        M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
+        carry_row, carry_val);
   ctx->launches++;
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;
@@ -576,15 +801,40 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
              float* carry_val, bool need_fixup, cudaStream_t stream) {
   int st;
   const int m = (int)M, nc = (int)n_chunks;
-  if (K == 32)
-    st = launch_balanced<8, 1, 8>(ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C,
-                                  chunk_start, chunk_row, carry_row, carry_val, stream);
-  else if (K == 64)
-    st = launch_balanced<16, 1, 8>(ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C,
-                                   chunk_start, chunk_row, carry_row, carry_val, stream);
-  else if (K == 128)
-    st = launch_balanced<32, 1, 8>(ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C,
-                                   chunk_start, chunk_row, carry_row, carry_val, stream);
+#define HPSPMM_ARGS ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, stream
+#define HPSPMM_WARGS ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, stream
+  static int variant = -1;
+  if (variant < 0) {
+    const char* e = getenv("HPSPMM_VARIANT");
+    variant = e ? atoi(e) : 0;
+  }
+  if (K == 32) {
+    if (rowsplit) st = launch_balanced<8, 1, 8, 4>(HPSPMM_ARGS);
+    else switch (variant) {
+      case 1: st = launch_warp<8, 8, 4>(HPSPMM_WARGS); break;
+      case 2: st = launch_warp<8, 2, 8>(HPSPMM_WARGS); break;
+      case 3: st = launch_warp<8, 4, 8>(HPSPMM_WARGS); break;
+      default: st = launch_warp<8, 4, 6>(HPSPMM_WARGS); break;
+    }
+  } else if (K == 64) {
+    if (rowsplit) st = launch_balanced<16, 1, 8, 4>(HPSPMM_ARGS);
+    else switch (variant) {
+      case 1: st = launch_warp<16, 8, 4>(HPSPMM_WARGS); break;
+      case 2: st = launch_warp<16, 2, 8>(HPSPMM_WARGS); break;
+      case 3: st = launch_warp<16, 4, 8>(HPSPMM_WARGS); break;
+      default: st = launch_warp<16, 4, 6>(HPSPMM_WARGS); break;
+    }
+  } else if (K == 128) {
+    if (rowsplit) st = launch_balanced<32, 1, 8, 4>(HPSPMM_ARGS);
+    else switch (variant) {
+      case 1: st = launch_warp<32, 8, 4>(HPSPMM_WARGS); break;
+      case 2: st = launch_warp<32, 2, 8>(HPSPMM_WARGS); break;
+      case 3: st = launch_warp<32, 4, 8>(HPSPMM_WARGS); break;
+      default: st = launch_warp<32, 4, 6>(HPSPMM_WARGS); break;
+    }
+  }
+#undef HPSPMM_ARGS
+#undef HPSPMM_WARGS
   else if ((K & 3) == 0)
     st = launch_generic<4>(ctx, rowsplit, m, (int)K, nc, row_ptr, col_idx, vals, B, C, chunk_start,
                            chunk_row, carry_row, carry_val, stream);

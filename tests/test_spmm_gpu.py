@@ -1,0 +1,184 @@
+"""Parity of the CUDA CSR SpMM with the CPU oracle, through the C ABI (needs a B200)."""
+import numpy as np
+import pytest
+
+from helpers import check_against_f64, csr_from_rows, gpu_spmm, random_csr
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(ctx, pkg, oracle, row_ptr, col_idx, vals, B, what, **kw):
+    C = gpu_spmm(ctx, pkg, row_ptr, col_idx, vals, B, **kw)
+    ref, abs_sum = oracle.spmm_f64(row_ptr, col_idx, vals, B)
+    errs = check_against_f64(C, ref, abs_sum, what)
+    return C, errs
+
+
+def test_cfg1_small_csr(gpu_ctx, pkg, oracle):
+    """BASELINE config 1: M=N=4096, degree U{1..32}, K=32, values and B in U(-1,1)."""
+    g = pkg.gen_uniform_degree(4096, 4096, 1, 32, seed=1, vals_kind=pkg.VALS_UPM1)
+    B = pkg.host_fill_uniform(4096 * 32, 1, 10, -1.0, 1.0).reshape(4096, 32)
+    C, _ = _check(gpu_ctx, pkg, oracle, g["row_ptr"], g["col_idx"], g["vals"], B, "cfg1")
+    ref32 = oracle.spmm_f32(g["row_ptr"], g["col_idx"], g["vals"], B)
+    # the reference checker's own criterion (max abs error < 0.1) holds with a wide margin
+    assert oracle.max_abs_err(C, ref32) < 1e-5
+    # the row-split algorithm sums every row in CSR order with FMAs: the fp32 oracle bit for bit
+    C2 = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B,
+                  opts=pkg.Opts(algo=pkg.ALGO_ROW_SPLIT))
+    assert np.array_equal(C2, ref32)
+
+
+@pytest.mark.parametrize("K", [32, 64, 128])
+@pytest.mark.parametrize("use_plan", [False, True])
+def test_power_law_heavy_rows(gpu_ctx, pkg, oracle, K, use_plan):
+    g = pkg.gen_rmat(14, 16, seed=2)
+    N = g["N"]
+    B = pkg.host_fill_uniform(N * K, 2, 10 + K, -1.0, 1.0).reshape(N, K)
+    deg = np.diff(g["row_ptr"])
+    assert deg.max() > 1000 and (deg == 0).sum() > 100   # heavy rows and empty rows both present
+    C, _ = _check(gpu_ctx, pkg, oracle, g["row_ptr"], g["col_idx"], g["vals"], B, "rmat14 K=%d" % K,
+                  use_plan=use_plan)
+    if K == 128:
+        # one lane group per warp: rows that fit in one chunk are summed in CSR order with
+        # FMAs, so they are bit-exact against the fp32 oracle
+        ref32 = oracle.spmm_f32(g["row_ptr"], g["col_idx"], g["vals"], B)
+        short = deg <= 128
+        assert np.array_equal(C[short], ref32[short])
+
+
+@pytest.mark.parametrize("K", [1, 3, 4, 7, 20, 33, 100, 160, 256, 516, 1000])
+def test_generic_widths(gpu_ctx, pkg, oracle, K):
+    rng = np.random.default_rng(K)
+    deg = rng.integers(0, 50, size=700)
+    deg[13] = 900
+    row_ptr, col_idx, vals = random_csr(700, 1000, deg, seed=K)
+    B = rng.uniform(-1, 1, size=(1000, K)).astype(np.float32)
+    _check(gpu_ctx, pkg, oracle, row_ptr, col_idx, vals, B, "generic K=%d" % K)
+
+
+@pytest.mark.parametrize("K", [32, 64, 128, 48])
+def test_edge_structures(gpu_ctx, pkg, oracle, K):
+    rng = np.random.default_rng(5)
+    N = 513
+    B = rng.uniform(-1, 1, size=(N, K)).astype(np.float32)
+    cases = {
+        "all rows empty": [[] for _ in range(300)],
+        "single entry": [[7]],
+        "single row with every entry": [list(range(N))],
+        "empty rows first and last": [[]] * 70 + [[1, 2, 3], [], [5]] + [[]] * 90,
+        "one heavy row between empties": [[]] * 40 + [list(range(0, N))] + [[]] * 40 + [[3]],
+        "two heavy rows back to back": [list(range(N)), list(range(1, N)), [0]],
+        "rows of length 127,128,129": [list(range(127)), list(range(128)), list(range(129)),
+                                        list(range(255)), list(range(256)), list(range(257))],
+        "dense-ish": [list(range(0, N, 2)) for _ in range(37)],
+    }
+    for name, rows in cases.items():
+        row_ptr, col_idx, vals = csr_from_rows(rows, N, rng)
+        _check(gpu_ctx, pkg, oracle, row_ptr, col_idx, vals, B, name + " K=%d" % K)
+        _check(gpu_ctx, pkg, oracle, row_ptr, col_idx, vals, B, name + " plan K=%d" % K, use_plan=True)
+
+
+def test_nnz_not_multiple_of_32_and_ragged_m(gpu_ctx, pkg, oracle):
+    for M, seed in ((1, 1), (3, 2), (257, 3), (1023, 4)):
+        rng = np.random.default_rng(seed)
+        deg = rng.integers(0, 9, size=M)
+        row_ptr, col_idx, vals = random_csr(M, 300, deg, seed)
+        B = rng.uniform(-1, 1, size=(300, 64)).astype(np.float32)
+        _check(gpu_ctx, pkg, oracle, row_ptr, col_idx, vals, B, "ragged M=%d" % M)
+
+
+@pytest.mark.parametrize("chunk", [32, 64, 512, 4096])
+def test_chunk_size_option(gpu_ctx, pkg, oracle, chunk):
+    g = pkg.gen_rmat(12, 16, seed=9)
+    B = pkg.host_fill_uniform(g["N"] * 64, 9, 1, -1.0, 1.0).reshape(g["N"], 64)
+    opts = pkg.Opts(algo=pkg.ALGO_BALANCED, chunk_nnz=chunk)
+    _check(gpu_ctx, pkg, oracle, g["row_ptr"], g["col_idx"], g["vals"], B, "chunk %d" % chunk, opts=opts)
+    _check(gpu_ctx, pkg, oracle, g["row_ptr"], g["col_idx"], g["vals"], B, "chunk %d plan" % chunk,
+           opts=opts, use_plan=True)
+
+
+@pytest.mark.parametrize("K", [32, 64, 128, 24])
+def test_row_split_algorithm_is_bit_exact(gpu_ctx, pkg, oracle, K):
+    """The GESpMM-shaped kernel sums every row in CSR order: identical bits to the fp32 oracle."""
+    g = pkg.gen_rmat(12, 16, seed=3)
+    B = pkg.host_fill_uniform(g["N"] * K, 3, K, -1.0, 1.0).reshape(g["N"], K)
+    opts = pkg.Opts(algo=pkg.ALGO_ROW_SPLIT)
+    C = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B, opts=opts)
+    assert np.array_equal(C, oracle.spmm_f32(g["row_ptr"], g["col_idx"], g["vals"], B))
+
+
+def test_run_to_run_determinism(gpu_ctx, pkg):
+    g = pkg.gen_rmat(14, 16, seed=6)
+    B = pkg.host_fill_uniform(g["N"] * 128, 6, 1, -1.0, 1.0).reshape(g["N"], 128)
+    first = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B)
+    for _ in range(3):
+        assert np.array_equal(first, gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B))
+    assert np.array_equal(first, gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B, use_plan=True))
+
+
+def test_overwrites_stale_output_and_linearity(gpu_ctx, pkg, oracle):
+    g = pkg.gen_uniform_degree(2000, 2000, 0, 20, seed=8)
+    rng = np.random.default_rng(8)
+    B1 = rng.uniform(-1, 1, size=(2000, 64)).astype(np.float32)
+    ones = np.ones((2000, 64), dtype=np.float32)
+    C1 = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], ones)
+    rowsum = np.add.reduceat(np.concatenate([g["vals"].astype(np.float64), [0.0]]),
+                             np.minimum(g["row_ptr"][:-1], g["nnz"]))
+    rowsum[np.diff(g["row_ptr"]) == 0] = 0
+    assert np.allclose(C1, rowsum[:, None], rtol=1e-5, atol=1e-5)       # A * ones = row sums
+    C2 = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B1)
+    C3 = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B1 + ones)
+    assert np.allclose(C3, C1 + C2, rtol=1e-4, atol=1e-4)              # linear in B
+
+
+def test_full_size_cfg2_k32(gpu_ctx, pkg, oracle):
+    """BASELINE config 2 at full size, K=32, against the oracle and by the row-sum property."""
+    g = pkg.gen_rmat(20, 16, seed=2)
+    K = 32
+    B = pkg.host_fill_uniform(g["N"] * K, 2, 32, -1.0, 1.0).reshape(g["N"], K)
+    C, errs = _check(gpu_ctx, pkg, oracle, g["row_ptr"], g["col_idx"], g["vals"], B, "cfg2 K=32",
+                     use_plan=True)
+    deg = np.diff(g["row_ptr"])
+    assert np.all(C[deg == 0] == 0)
+
+
+def test_host_buffer_entry_point(gpu_ctx, pkg, oracle):
+    g = pkg.gen_rmat(12, 16, seed=4)
+    K = 64
+    B = pkg.host_fill_uniform(g["N"] * K, 4, 1, -1.0, 1.0).reshape(g["N"], K)
+    C = np.full((g["M"], K), np.nan, dtype=np.float32)
+    gpu_ctx.spmm_csr_host(g["M"], g["N"], K, g["nnz"], g["row_ptr"], g["col_idx"], g["vals"], B, C)
+    ref, abs_sum = oracle.spmm_f64(g["row_ptr"], g["col_idx"], g["vals"], B)
+    check_against_f64(C, ref, abs_sum, "host entry")
+
+
+def test_argument_errors_return_codes(gpu_ctx, pkg):
+    lib = pkg.load_library()
+    d = gpu_ctx.alloc((64,), np.float32)
+    h = gpu_ctx.handle
+    f = lib.hpspmm_spmm_csr_f32
+    assert f(h, None, 4, 4, 0, 0, d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, None, None) == pkg.ERR_INVALID   # K = 0
+    assert f(h, None, -1, 4, 32, 0, d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, None, None) == pkg.ERR_INVALID
+    assert f(h, None, 4, 4, 32, 0, None, d.ptr, d.ptr, d.ptr, d.ptr, None, None) == pkg.ERR_INVALID  # null row_ptr
+    assert f(h, None, 4, 4, 32, 8, d.ptr, d.ptr, d.ptr, d.ptr + 4, d.ptr, None, None) == pkg.ERR_INVALID  # misaligned B
+    assert f(h, None, 1 << 40, 4, 32, 0, d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, None, None) == pkg.ERR_UNSUPPORTED
+    assert f(None, None, 4, 4, 32, 0, d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, None, None) == pkg.ERR_INVALID
+    assert b"invalid" in lib.hpspmm_last_error(h) or b"sizes" in lib.hpspmm_last_error(h)
+    bad_algo = pkg.Opts(algo=99)
+    rp = gpu_ctx.upload(np.zeros(5, dtype=np.int32))
+    import ctypes
+    assert f(h, None, 4, 4, 32, 0, rp.ptr, d.ptr, d.ptr, d.ptr, d.ptr, ctypes.byref(bad_algo), None) == pkg.ERR_INVALID
+    d.free()
+    rp.free()
+
+
+def test_fill_factories_match_host(gpu_ctx, pkg):
+    n = 100_003
+    d = gpu_ctx.alloc((n,), np.float32)
+    gpu_ctx.fill_uniform(d, n, 42, 7, -1.0, 1.0)
+    assert np.array_equal(d.to_host(), pkg.host_fill_uniform(n, 42, 7, -1.0, 1.0))   # bit exact
+    gpu_ctx.fill_uniform(d, n, 42, 8, 0.0, 1.0)
+    assert np.array_equal(d.to_host(), pkg.host_fill_uniform(n, 42, 8, 0.0, 1.0))
+    gpu_ctx.fill(d, n, 2.5)
+    assert np.all(d.to_host() == 2.5)
+    d.free()
