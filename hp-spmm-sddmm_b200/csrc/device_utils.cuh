@@ -18,10 +18,10 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
   return p;
 }
 
-// 16-byte read-only gather of a dense row fragment, kept in L1 and L2 as long as possible.
+// 16-byte read-only gather of a dense row fragment with an L2 residency policy attached.
 __device__ __forceinline__ float4 ld_gather_keep(const float* p, uint64_t policy) {
   float4 v;
-  asm("ld.global.nc.L1::evict_last.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+  asm("ld.global.nc.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
       : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
       : "l"(p), "l"(policy));
   return v;

@@ -219,7 +219,8 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
   }
   hpspmm_device_guard guard(ctx->device);
   cudaStream_t s = (cudaStream_t)stream;
-  const bool hint = !(opts && opts->b_l2_hint == 1);
+  const int hint_mode = opts ? opts->b_l2_hint : 0;
+  const bool hint = hint_mode == 2 || (hint_mode == 0 && K >= 64);
   const int32_t* chunk_start;
   const int32_t* chunk_row;
   int64_t n_chunks;

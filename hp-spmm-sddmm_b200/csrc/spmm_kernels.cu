@@ -328,14 +328,32 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   const float* Bl = B + l * 4;
 
-  // the row is complete: combine the groups' partial sums, store, start the next row
+  // the row is complete: combine the groups' partial sums, store, start the next row.
+  // The common case (the next row is not empty, or only a few are) stays inline; a long
+  // run of empty rows falls back to a binary search.
   auto finish_row = [&](int next_entry) {
     const float4 t = reduce_groups<W>(acc);
     if (g == 0) st_stream(C + (int64_t)row * K + l * 4, t);
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const unsigned long long nr = next_row_packed(row_ptr, M, next_entry, row);
-    row = (int)(unsigned)nr;
-    row_end = (int)(nr >> 32);
+    int e, probes = 0;
+    do {
+      ++row;
+      e = __ldg(row_ptr + row + 1);
+    } while (e == next_entry && ++probes < 16);
+    if (e == next_entry) {
+      // a long run of empty rows: binary search for the row that holds next_entry
+      int lo = row + 1, hi = M + 1;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(row_ptr + mid) <= next_entry)
+          lo = mid + 1;
+        else
+          hi = mid;
+      }
+      row = lo - 1;
+      e = __ldg(row_ptr + row + 1);
+    }
+    row_end = e;
   };
 
   int stage = 0;
@@ -757,9 +775,9 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 }  // namespace
 
 int32_t hpspmm_default_chunk_nnz(int64_t K) {
-  if (K <= 32) return 128;
-  if (K <= 64) return 128;
-  return 256;
+  // measured on B200 (R-MAT scale 20): 128 beats 64, 256 and 512 at K = 32, 64 and 128
+  (void)K;
+  return 128;
 }
 
 int hpspmm_launch_chunk_table(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
@@ -812,25 +830,31 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
     if (rowsplit) st = launch_balanced<8, 1, 8, 4>(HPSPMM_ARGS);
     else switch (variant) {
       case 1: st = launch_warp<8, 8, 4>(HPSPMM_WARGS); break;
-      case 2: st = launch_warp<8, 2, 8>(HPSPMM_WARGS); break;
-      case 3: st = launch_warp<8, 4, 8>(HPSPMM_WARGS); break;
-      default: st = launch_warp<8, 4, 6>(HPSPMM_WARGS); break;
+      case 2: st = launch_warp<8, 4, 6>(HPSPMM_WARGS); break;
+      case 3: st = launch_warp<8, 8, 3>(HPSPMM_WARGS); break;
+      case 4: st = launch_warp<8, 4, 4>(HPSPMM_WARGS); break;
+      case 5: st = launch_warp<8, 2, 8>(HPSPMM_WARGS); break;
+      default: st = launch_warp<8, 4, 5>(HPSPMM_WARGS); break;
     }
   } else if (K == 64) {
     if (rowsplit) st = launch_balanced<16, 1, 8, 4>(HPSPMM_ARGS);
     else switch (variant) {
       case 1: st = launch_warp<16, 8, 4>(HPSPMM_WARGS); break;
-      case 2: st = launch_warp<16, 2, 8>(HPSPMM_WARGS); break;
-      case 3: st = launch_warp<16, 4, 8>(HPSPMM_WARGS); break;
-      default: st = launch_warp<16, 4, 6>(HPSPMM_WARGS); break;
+      case 2: st = launch_warp<16, 4, 6>(HPSPMM_WARGS); break;
+      case 3: st = launch_warp<16, 8, 3>(HPSPMM_WARGS); break;
+      case 4: st = launch_warp<16, 4, 4>(HPSPMM_WARGS); break;
+      case 5: st = launch_warp<16, 2, 8>(HPSPMM_WARGS); break;
+      default: st = launch_warp<16, 4, 5>(HPSPMM_WARGS); break;
     }
   } else if (K == 128) {
     if (rowsplit) st = launch_balanced<32, 1, 8, 4>(HPSPMM_ARGS);
     else switch (variant) {
       case 1: st = launch_warp<32, 8, 4>(HPSPMM_WARGS); break;
-      case 2: st = launch_warp<32, 2, 8>(HPSPMM_WARGS); break;
-      case 3: st = launch_warp<32, 4, 8>(HPSPMM_WARGS); break;
-      default: st = launch_warp<32, 4, 6>(HPSPMM_WARGS); break;
+      case 2: st = launch_warp<32, 4, 6>(HPSPMM_WARGS); break;
+      case 3: st = launch_warp<32, 8, 3>(HPSPMM_WARGS); break;
+      case 4: st = launch_warp<32, 4, 4>(HPSPMM_WARGS); break;
+      case 5: st = launch_warp<32, 2, 8>(HPSPMM_WARGS); break;
+      default: st = launch_warp<32, 4, 5>(HPSPMM_WARGS); break;
     }
   }
 #undef HPSPMM_ARGS
@@ -938,7 +962,8 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
   if (M == 0) return HPSPMM_OK;
   hpspmm_device_guard guard(ctx->device);
   cudaStream_t s = (cudaStream_t)stream;
-  const bool hint = !(opts && opts->b_l2_hint == 1);
+  const int hint_mode = opts ? opts->b_l2_hint : 0;
+  const bool hint = hint_mode == 2 || (hint_mode == 0 && K >= 64);
   const int algo = opts ? opts->algo : HPSPMM_ALGO_AUTO;
   if (algo == HPSPMM_ALGO_ROW_SPLIT) {
     return run_spmm(ctx, hint, true, M, K, M, row_ptr, col_idx, vals, B, C, nullptr, nullptr,
