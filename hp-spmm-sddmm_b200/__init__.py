@@ -89,6 +89,8 @@ PROTOTYPES = {
     "hpspmm_plan_create": (c_int, [_P, _I64, _I64, _P, _I64, POINTER(Opts), _P, POINTER(_P)]),
     "hpspmm_plan_destroy": (c_int, [_P, _P]),
     "hpspmm_plan_info": (c_int, [_P, POINTER(_I64), POINTER(_I64), POINTER(_I64), POINTER(_I64)]),
+    "hpspmm_spmm_csr_f32_static_scratch": (c_int, [c_int, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P,
+                                                   ctypes.c_char_p, c_size_t]),
     "hpspmm_spmm_csr_f32_host": (c_int, [_P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P,
                                          POINTER(Opts)]),
     "hpspmm_spmm_coo_f32": (c_int, [_P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, POINTER(Opts), _P]),

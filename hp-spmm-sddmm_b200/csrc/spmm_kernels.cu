@@ -19,6 +19,7 @@
 // HPSPMM_ALGO_ROW_SPLIT keeps the reference's GESpMM shape (one sub-warp per row, every row
 // summed in storage order), which reproduces the CPU oracle bit for bit.
 #include <cstdlib>
+#include <mutex>
 #include <new>
 
 #include "device_utils.cuh"
@@ -1078,3 +1079,113 @@ int hpspmm_spmm_coo_f32(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_
 }
 
 }  // extern "C"
+
+// ---- CSR SpMM with its scratch in a static device array -----------------------------------
+// Some callers must not allocate device memory at the moment they need a product: the
+// enqueue hook of an inference-runtime plugin, a step inside a serving loop whose framework
+// allocator already owns every byte of the device, or code on a latency budget that cannot
+// afford the device-wide synchronisation an allocation may cause.  For them the chunk table
+// and the carry slots live in the array below instead of in context-owned scratch.  The
+// array is part of the library image: every GPU that loads the library holds these bytes
+// until the process exits, which is why the limit is modest.
+#define HPSPMM_STATIC_SCRATCH_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[HPSPMM_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kMaxStaticDevices = 64;
+struct static_scratch_state {
+  bool ready;
+  unsigned char* base;  // device address of g_static_scratch on this device
+  int sm_count;
+};
+static_scratch_state g_static_state[kMaxStaticDevices];
+std::mutex g_static_mutex;
+
+void write_err(char* buf, size_t len, const char* msg) {
+  if (buf && len) snprintf(buf, len, "%s", msg);
+}
+
+}  // namespace
+
+extern "C" int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M, int64_t N,
+                                                  int64_t K, int64_t nnz, const int32_t* row_ptr,
+                                                  const int32_t* col_idx, const float* vals,
+                                                  const float* B, float* C, hpspmm_stream stream,
+                                                  char* err_buf, size_t err_len) {
+  if (err_buf && err_len) err_buf[0] = 0;
+  if (device_ordinal < 0 || device_ordinal >= kMaxStaticDevices) {
+    write_err(err_buf, err_len, "device ordinal out of range");
+    return HPSPMM_ERR_INVALID;
+  }
+  hpspmm_ctx local;  // a stack stand-in for a context: no allocation behind it
+  memset(&local, 0, sizeof(local));
+  local.device = device_ordinal;
+  int st = check_spmm_args(&local, M, N, K, nnz, row_ptr, col_idx, vals, B, C);
+  if (st != HPSPMM_OK) {
+    write_err(err_buf, err_len, local.err);
+    return st;
+  }
+  if (M == 0) return HPSPMM_OK;
+
+  const int32_t S = hpspmm_default_chunk_nnz(K);
+  const int64_t n_chunks = (nnz + S - 1) / S;
+  const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
+  const size_t b_cval = align_up((size_t)(n_chunks + 1) * (size_t)K * 4, 256);
+  const size_t need = 3 * b_int + b_cval;
+  if (need > (size_t)HPSPMM_STATIC_SCRATCH_BYTES) {
+    char msg[256];
+    const long long max_chunks = (long long)(HPSPMM_STATIC_SCRATCH_BYTES - 4 * 256) / (12 + 4 * K) - 1;
+    snprintf(msg, sizeof(msg),
+             "matrix too large for the static scratch: nnz = %lld at K = %lld needs %zu bytes, the "
+             "array holds %u (about %lld nnz at this K); use hpspmm_spmm_csr_f32 instead",
+             (long long)nnz, (long long)K, need, (unsigned)HPSPMM_STATIC_SCRATCH_BYTES,
+             max_chunks > 0 ? max_chunks * S : 0ll);
+    write_err(err_buf, err_len, msg);
+    return HPSPMM_ERR_UNSUPPORTED;
+  }
+
+  hpspmm_device_guard guard(device_ordinal);  // the device is current from here on
+  static_scratch_state& state = g_static_state[device_ordinal];
+  {
+    // Once per device: the array's name is a host-side handle, not a device address, so ask
+    // the runtime where the array lives on the current device.
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!state.ready) {
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        char msg[200];
+        snprintf(msg, sizeof(msg), "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+        write_err(err_buf, err_len, msg);
+        return HPSPMM_ERR_CUDA;
+      }
+      int sms = 0;
+      e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_ordinal);
+      if (e != cudaSuccess || sms <= 0) {
+        write_err(err_buf, err_len, "cudaDeviceGetAttribute(multiprocessor count) failed");
+        return HPSPMM_ERR_CUDA;
+      }
+      state.base = (unsigned char*)p;
+      state.sm_count = sms;
+      state.ready = true;
+    }
+  }
+  local.sm_count = state.sm_count;
+
+  // Every call rewrites the whole chunk table and every carry_row entry it later reads, and
+  // a carry_val slot is read only where this call's carry_row names a row, so nothing left
+  // over from an earlier call is ever consumed and nothing needs clearing first.
+  int32_t* chunk_start = (int32_t*)state.base;
+  int32_t* chunk_row = (int32_t*)(state.base + b_int);
+  int32_t* carry_row = (int32_t*)(state.base + 2 * b_int);
+  float* carry_val = (float*)(state.base + 3 * b_int);
+  cudaStream_t s = (cudaStream_t)stream;
+  st = hpspmm_launch_chunk_table(&local, M, nnz, row_ptr, S, n_chunks, chunk_start, chunk_row,
+                                 nullptr, s);
+  if (st == HPSPMM_OK)
+    st = run_spmm(&local, K >= 64, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
+                  chunk_row, carry_row, carry_val, true, s);
+  if (st != HPSPMM_OK) write_err(err_buf, err_len, local.err);
+  return st;
+}

@@ -147,6 +147,34 @@ HPSPMM_API int hpspmm_plan_info(const hpspmm_plan* plan, int64_t* n_chunks,
                                 int64_t* n_split_chunks, int64_t* chunk_nnz,
                                 int64_t* scratch_bytes);
 
+/* The same product for callers that cannot allocate device memory when they need it.
+ * (No counterpart in the reference, whose entry points allocate nothing because its
+ * kernels need no scratch.)  Typical callers: the enqueue hook of an inference-runtime
+ * plugin, which is forbidden to allocate; a process whose framework allocator has already
+ * reserved the whole device, so that cudaMalloc would fail; a latency-critical loop that
+ * cannot take the device-wide synchronisation an allocation may bring.
+ *
+ * This entry point calls no cudaMalloc, cudaFree or allocating library routine, and needs
+ * no context.  The chunk table and the carry slots of the nnz-balanced kernel live in one
+ * 16 MiB array inside the library image, so every GPU that loads the library gives up
+ * 16 MiB until the process exits.  A matrix whose scratch would not fit -- more than
+ * (16 MiB - 1 KiB) / (12 + 4 K) chunks of 128 nnz: about 15 M nnz at K = 32, 8 M at
+ * K = 64, 4 M at K = 128 -- is refused with HPSPMM_ERR_UNSUPPORTED and a message in
+ * err_buf; use hpspmm_spmm_csr_f32 for it.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress,
+ * once per device, with that device current).  Make that first call at start-up, before
+ * any stream capture begins.  All calls on one device share the array: two calls that
+ * overlap on the GPU (different streams, or different host threads) race on it, so
+ * serialise them.  Nothing has to be cleared between calls: each call rewrites everything
+ * it later reads.  Pointers are device pointers on device_ordinal; results equal those of
+ * hpspmm_spmm_csr_f32 with default options bit for bit.  err_buf may be NULL. */
+HPSPMM_API int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M, int64_t N,
+                                                  int64_t K, int64_t nnz, const int32_t* row_ptr,
+                                                  const int32_t* col_idx, const float* vals,
+                                                  const float* B, float* C, hpspmm_stream stream,
+                                                  char* err_buf, size_t err_len);
+
 /* Same product with HOST buffers: copies A and B to the device, runs the product,
  * copies C back, synchronises.  This is the call the end-to-end figure is timed
  * through; it is what the reference's driver does around GESpMM
