@@ -1,0 +1,90 @@
+// Comparator shim (test infrastructure, never part of the product): exposes the REFERENCE's
+// own GESpMM and LBSpMM, compiled from the reference's sources where they lie, behind two
+// C functions that take host arrays.  Used once on a B200 to produce the golden vectors under
+// tests/golden/ and, optionally, as a live second opinion in GPU tests.
+//
+// Nothing of the reference is copied: this file only includes its headers and calls its
+// entry points (include/spmm/mm/spmm_kernel.h:19-21).
+#include <cstring>
+
+#include "spmm/mm/spmm_kernel.h"
+
+namespace {
+
+Matrix host_ints(const int* src, int n) {
+  Matrix m({n}, Device(kCPU), DataType(kInt32));
+  std::memcpy(m.mutable_data<int>(), src, sizeof(int) * (size_t)n);
+  return m;
+}
+
+Matrix host_floats(const float* src, int rows, int cols) {
+  Matrix m = cols > 0 ? Matrix({rows, cols}, Device(kCPU), DataType(kFloat))
+                      : Matrix({rows}, Device(kCPU), DataType(kFloat));
+  std::memcpy(m.mutable_data<float>(), src, sizeof(float) * (size_t)rows * (size_t)(cols > 0 ? cols : 1));
+  return m;
+}
+
+}  // namespace
+
+extern "C" {
+
+// number of launches the reference's entry points run per call (include/spmm/utils/timer_cuda.h:4)
+__attribute__((visibility("default"))) int ref_launches_per_call(void) { return EXE_NUM_CUDA; }
+
+// C_out = GESpMM(A, B): overwrite semantics, so the 200 launches leave one product.
+__attribute__((visibility("default"))) int ref_gespmm(int m, int n, int k, int nnz, const int* row_ptr,
+                                                      const int* col_idx, const float* vals,
+                                                      const float* B, float* C_out, float* ms_out) {
+  CSR_Matrix h;
+  h.num_rows_ = m;
+  h.num_cols_ = n;
+  h.num_nonzeros_ = nnz;
+  h.row_offsets_ = host_ints(row_ptr, m + 1);
+  h.column_indices_ = host_ints(col_idx, nnz);
+  h.values_ = host_floats(vals, nnz, 0);
+  // spmm_common.cpp (home of csr_to_cuda) is not compiled -- it also holds the cusp-based
+  // loaders -- so the three members are moved to the device here with the same Matrix::to
+  CSR_Matrix d = h;
+  d.row_offsets_ = h.row_offsets_.to(kCUDA);
+  d.column_indices_ = h.column_indices_.to(kCUDA);
+  d.values_ = h.values_.to(kCUDA);
+  Matrix dB = host_floats(B, n, k).to(kCUDA);
+  Matrix dC = full({m, k}, Device(kCUDA), DataType(kFloat), 0.0);
+  float ms = 0.f;
+  GESpMM(d, dB, dC, ms);
+  if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  Matrix hC = dC.to(kCPU);
+  std::memcpy(C_out, hC.data<float>(), sizeof(float) * (size_t)m * (size_t)k);
+  if (ms_out) *ms_out = ms;
+  return 0;
+}
+
+// C_out = what LBSpMM leaves in a zeroed C: EXE_NUM_CUDA accumulated products (the caller
+// divides, as the reference's checker does, spmm/utils/compare.cpp:12-13).
+__attribute__((visibility("default"))) int ref_lbspmm(int m, int n, int k, int nnz_padded, const int* row_idx,
+                                                      const int* col_idx, const float* vals,
+                                                      const float* B, float* C_out, float* ms_out) {
+  COO_Matrix h;
+  h.num_rows_ = m;
+  h.num_cols_ = n;
+  h.num_nonzeros_ = nnz_padded;
+  h.row_indices_ = host_ints(row_idx, nnz_padded);
+  h.column_indices_ = host_ints(col_idx, nnz_padded);
+  h.values_ = host_floats(vals, nnz_padded, 0);
+  COO_Matrix d = h;
+  d.row_indices_ = h.row_indices_.to(kCUDA);
+  d.column_indices_ = h.column_indices_.to(kCUDA);
+  d.values_ = h.values_.to(kCUDA);
+  Matrix dB = host_floats(B, n, k).to(kCUDA);
+  Matrix dC = full({m, k}, Device(kCUDA), DataType(kFloat), 0.0);
+  float ms = 0.f;
+  fill_matrix(dC, 0.0f);
+  LBSpMM(d, dB, dC, ms);
+  if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  Matrix hC = dC.to(kCPU);
+  std::memcpy(C_out, hC.data<float>(), sizeof(float) * (size_t)m * (size_t)k);
+  if (ms_out) *ms_out = ms;
+  return 0;
+}
+
+}  // extern "C"

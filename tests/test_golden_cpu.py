@@ -1,0 +1,45 @@
+"""The CPU oracle against golden vectors produced by the reference's own kernels (no GPU needed)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+CASES = ["uniform512_k32", "rmat9_k64", "rmat8_k128"]
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_oracle_equals_reference_gespmm_bit_for_bit(oracle, name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    got = oracle.spmm_f32(z["row_ptr"], z["col_idx"], z["vals"], z["B"])
+    assert np.array_equal(got, z["C_gespmm"])
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_oracle_matches_reference_lbspmm(oracle, name):
+    """LBSpMM's atomics fix no summation order: tolerance, plus the reference's own 0.1 criterion."""
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    ref64, abs_sum = oracle.spmm_f64(z["row_ptr"], z["col_idx"], z["vals"], z["B"])
+    err = np.max(np.abs(z["C_lbspmm_div200"] - ref64) / np.maximum(abs_sum, 1e-30))
+    assert err <= 1e-5
+    assert oracle.max_abs_err(z["C_lbspmm_div200"], oracle.spmm_f32(z["row_ptr"], z["col_idx"], z["vals"], z["B"])) < 0.1
+    # the COO restatement on the padded arrays gives the same product
+    r, c, v = oracle.csr_to_coo_padded(z["row_ptr"], z["col_idx"], z["vals"], 32)
+    coo = oracle.spmm_coo_f32(len(z["row_ptr"]) - 1, r, c, v, z["B"])
+    assert np.max(np.abs(coo - z["C_lbspmm_div200"]) / np.maximum(abs_sum, 1e-30)) <= 1e-5
+
+
+def test_cfg1_full_size_against_reference_rows(pkg, oracle):
+    z = np.load(os.path.join(GOLDEN, "cfg1_sampled_rows.npz"))
+    g = pkg.gen_uniform_degree(4096, 4096, 1, 32, seed=1, vals_kind=pkg.VALS_UPM1)
+    B = pkg.host_fill_uniform(4096 * 32, 1, 10, -1.0, 1.0).reshape(4096, 32)
+    C = oracle.spmm_f32(g["row_ptr"], g["col_idx"], g["vals"], B)
+    assert np.array_equal(C[z["rows"]], z["C_gespmm"])
+    assert np.allclose(C.astype(np.float64).sum(axis=0), z["col_sum_gespmm"], rtol=0, atol=1e-9)
+    assert np.allclose(C[z["rows"]], z["C_lbspmm_div200"], rtol=1e-4, atol=1e-5)
+
+
+def test_summary_records_bit_equality():
+    s = json.load(open(os.path.join(GOLDEN, "summary.json")))
+    assert all(v["gespmm_equals_fp32_oracle"] for v in s.values())

@@ -1,0 +1,92 @@
+"""Multi-GPU row sharding on CPU: the partitioner, and a world-size-2 gloo run in which every
+rank multiplies its shard with the CPU oracle and the gathered C equals the unsharded product."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, b_sharded, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    import oracle_lib
+    pkg = entry.load_package()
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = pkg.gen_rmat(11, 16, seed=21)
+    K = 32
+    bounds = pkg.shard_bounds(g["row_ptr"], world)
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    rp, ci, v = pkg.shard_csr(g["row_ptr"], g["col_idx"], g["vals"], lo, hi)
+    if b_sharded:
+        # B is produced row-sharded with the same boundaries (a GNN layer's output): all-gather it
+        mine = pkg.host_fill_uniform(g["N"] * K, 21, 1, -1.0, 1.0).reshape(g["N"], K)[lo:hi]
+        sizes = [int(bounds[r + 1] - bounds[r]) for r in range(world)]
+        parts = [torch.empty((s, K), dtype=torch.float32) for s in sizes]
+        pad = max(sizes)
+        padded = torch.zeros((pad, K), dtype=torch.float32)
+        padded[:hi - lo] = torch.from_numpy(np.ascontiguousarray(mine))
+        gathered = [torch.empty((pad, K), dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(gathered, padded)
+        B = torch.cat([gathered[r][:sizes[r]] for r in range(world)]).numpy()
+    else:
+        B = pkg.host_fill_uniform(g["N"] * K, 21, 1, -1.0, 1.0).reshape(g["N"], K)   # replicated
+    C_local = oracle_lib.spmm_f32(rp, ci, v, B)
+    np.save(os.path.join(out_dir, "c_%d.npy" % rank), C_local)
+    np.save(os.path.join(out_dir, "nnz_%d.npy" % rank), np.array([len(ci)]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("b_sharded", [False, True])
+def test_two_rank_row_sharding_gloo(tmp_path, pkg, oracle, b_sharded):
+    import torch.multiprocessing as mp
+    port = _free_port()
+    mp.spawn(_rank_main, args=(2, port, b_sharded, str(tmp_path)), nprocs=2, join=True)
+    g = pkg.gen_rmat(11, 16, seed=21)
+    B = pkg.host_fill_uniform(g["N"] * 32, 21, 1, -1.0, 1.0).reshape(g["N"], 32)
+    want = oracle.spmm_f32(g["row_ptr"], g["col_idx"], g["vals"], B)
+    got = np.concatenate([np.load(tmp_path / ("c_%d.npy" % r)) for r in range(2)])
+    assert np.array_equal(got, want)          # row blocks are independent: bit-identical
+    nnz = [int(np.load(tmp_path / ("nnz_%d.npy" % r))[0]) for r in range(2)]
+    assert sum(nnz) == g["nnz"] and abs(nnz[0] - nnz[1]) <= 2 * np.diff(g["row_ptr"]).max()
+
+
+def test_shards_tile_the_matrix_for_every_world_size(pkg, oracle):
+    g = pkg.gen_erdos_renyi(5000, 5000, 20.0, seed=22)
+    B = pkg.host_fill_uniform(5000 * 32, 22, 1, -1.0, 1.0).reshape(5000, 32)
+    want = oracle.spmm_f32(g["row_ptr"], g["col_idx"], g["vals"], B)
+    for G in (1, 2, 3, 4, 8):
+        bounds = pkg.shard_bounds(g["row_ptr"], G)
+        parts = []
+        for r in range(G):
+            rp, ci, v = pkg.shard_csr(g["row_ptr"], g["col_idx"], g["vals"], int(bounds[r]), int(bounds[r + 1]))
+            parts.append(oracle.spmm_f32(rp, ci, v, B))
+        assert np.array_equal(np.concatenate(parts), want)
+        sizes = np.diff(g["row_ptr"][bounds])
+        assert sizes.max() - sizes.min() <= 2 * np.diff(g["row_ptr"]).max()
+
+
+def test_degenerate_shards(pkg):
+    rp = np.array([0, 0, 0, 5, 5], dtype=np.int32)      # one non-empty row, four shards
+    b = pkg.shard_bounds(rp, 4)
+    assert b[0] == 0 and b[-1] == 4 and np.all(np.diff(b) >= 0)
+    assert sum(int(rp[b[i + 1]] - rp[b[i]]) for i in range(4)) == 5
+    empty = np.zeros(7, dtype=np.int32)
+    assert list(pkg.shard_bounds(empty, 3)) == [0, 0, 0, 6]
