@@ -66,10 +66,10 @@ __global__ void chunk_table_kernel(int M, int nnz, const int* __restrict__ row_p
 // Blocks past the chunk blocks walk all rows and write zeros into the empty ones.
 __device__ __forceinline__ void zero_empty_rows(int M, int K, const int* __restrict__ row_ptr,
                                                 float* __restrict__ C, int zero_block,
-                                                int n_zero_blocks) {
+                                                int n_zero_blocks, int block_threads = kBlockThreads) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int warps_per_block = kBlockThreads / 32;
+  const int warps_per_block = block_threads / 32;
   const int64_t stride = (int64_t)n_zero_blocks * warps_per_block * 32;
   for (int64_t r0 = ((int64_t)zero_block * warps_per_block + warp) * 32; r0 < M; r0 += stride) {
     const int64_t r = r0 + lane;
@@ -281,8 +281,8 @@ __device__ __forceinline__ float4 reduce_groups(float4 a) {
   return a;
 }
 
-template <int W, int U, int MINB, bool HINT>
-__global__ void __launch_bounds__(kBlockThreads, MINB)
+template <int W, int U, int MINB, bool HINT, int BT>
+__global__ void __launch_bounds__(BT, MINB)
 spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict__ row_ptr,
                  const int* __restrict__ col_idx, const float* __restrict__ vals,
                  const float* __restrict__ B, float* __restrict__ C,
@@ -294,16 +294,16 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   constexpr int BATCH = U * G;   // entries per batch of gathers
   constexpr int STAGES = 2;
   static_assert(BATCH <= T && T % BATCH == 0, "batch must tile the staged tile");
-  __shared__ int2 tiles[kBlockThreads / 32][STAGES][T];
+  __shared__ int2 tiles[BT / 32][STAGES][T];
 
   if ((int)blockIdx.x >= n_chunk_blocks) {
-    zero_empty_rows(M, K, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks);
+    zero_empty_rows(M, K, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks, BT);
     return;
   }
   const int lane = threadIdx.x & 31;
   const int g = lane / W;   // group
   const int l = lane % W;   // position inside the group = float4 column
-  const int chunk = (int)(((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) >> 5);
+  const int chunk = (int)(((int64_t)blockIdx.x * BT + threadIdx.x) >> 5);
   if (chunk >= n_chunks) return;
   const uint64_t policy = HINT ? policy_evict_last() : 0ull;
   int2(*my)[T] = tiles[threadIdx.x >> 5];
@@ -361,34 +361,53 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   for (int base = n0; base < n1; base += T) {
     cp_async_wait<STAGES - 1>();
     __syncwarp();
-#pragma unroll 1
-    for (int u0 = 0; u0 < T; u0 += BATCH) {
-      const int j0 = base + u0;
-      if (j0 >= n1) break;
-      float4 b[U];
-      float v[U];
+    const int2* tile = &my[stage][g];
+    if (base + T <= n1 && row_end >= base + T) {
+      // Fast tile: all 32 entries belong to the current row.  Fully unrolled, every
+      // shared-memory offset is a compile-time constant, no tests between gathers.
 #pragma unroll
-      for (int i = 0; i < U; ++i) {
-        const int2 e = my[stage][u0 + i * G + g];   // one broadcast per group
-        v[i] = __int_as_float(e.y);
-        b[i] = ld_gather<HINT>(Bl + (int64_t)e.x * K, policy);
-      }
-      if (j0 + BATCH <= n1 && row_end >= j0 + BATCH) {
-#pragma unroll
-        for (int i = 0; i < U; ++i) fma4(acc, v[i], b[i]);
-      } else {
+      for (int s0 = 0; s0 < T / G; s0 += U) {
+        float4 b[U];
+        float v[U];
 #pragma unroll
         for (int i = 0; i < U; ++i) {
-          const int lo = j0 + i * G;
-          const int hi = min(lo + G, n1);
-          const int mine = lo + g;
-          int cur = lo;
-          while (row_end < hi) {   // warp-uniform: the current row ends inside this step
-            if (mine >= cur && mine < row_end) fma4(acc, v[i], b[i]);
-            cur = row_end;
-            finish_row(cur);
+          const int2 e = tile[(s0 + i) * G];   // one broadcast per group
+          v[i] = __int_as_float(e.y);
+          b[i] = ld_gather<HINT>(Bl + (int64_t)e.x * K, policy);
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i) fma4(acc, v[i], b[i]);
+      }
+    } else {
+#pragma unroll 1
+      for (int u0 = 0; u0 < T; u0 += BATCH) {
+        const int j0 = base + u0;
+        if (j0 >= n1) break;
+        float4 b[U];
+        float v[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+          const int2 e = tile[u0 + i * G];
+          v[i] = __int_as_float(e.y);
+          b[i] = ld_gather<HINT>(Bl + (int64_t)e.x * K, policy);
+        }
+        if (j0 + BATCH <= n1 && row_end >= j0 + BATCH) {
+#pragma unroll
+          for (int i = 0; i < U; ++i) fma4(acc, v[i], b[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < U; ++i) {
+            const int lo = j0 + i * G;
+            const int hi = min(lo + G, n1);
+            const int mine = lo + g;
+            int cur = lo;
+            while (row_end < hi) {   // warp-uniform: the current row ends inside this step
+              if (mine >= cur && mine < row_end) fma4(acc, v[i], b[i]);
+              cur = row_end;
+              finish_row(cur);
+            }
+            if (mine >= cur && mine < hi) fma4(acc, v[i], b[i]);
           }
-          if (mine >= cur && mine < hi) fma4(acc, v[i], b[i]);
         }
       }
     }
@@ -524,8 +543,47 @@ spmm_generic_kernel(int M, int K, int n_chunks, int n_chunk_blocks, const int* _
 
 // ---- carries ---------------------------------------------------------------------------
 // One lane per chunk finds the first carry of each split row; the warp then counts that
-// row's carries (32 at a time), sums them in chunk order with independent loads, and adds
-// the total to the row its owner stored.
+// row's carries (32 at a time) and sums them.  For K = 4*W <= 128 the warp works as
+// G = 32/W lane groups: group g sums carries g, g+G, ... four at a time with independent
+// loads, the groups are combined in a fixed order, and the total is added to the row its
+// owner stored.  The order of additions depends only on the chunking, never on timing.
+template <int W>
+__device__ __forceinline__ void add_carries_grouped(const float* __restrict__ src, int64_t len, int K,
+                                                    float* __restrict__ crow, int lane) {
+  constexpr int G = 32 / W;
+  const int g = lane / W, l = lane % W;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  int64_t i = g;
+  for (; i + 3 * G < len; i += 4 * G) {
+    float4 t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t[u] = *reinterpret_cast<const float4*>(src + (i + u * G) * K + l * 4);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s.x += t[u].x;
+      s.y += t[u].y;
+      s.z += t[u].z;
+      s.w += t[u].w;
+    }
+  }
+  for (; i < len; i += G) {
+    const float4 t = *reinterpret_cast<const float4*>(src + i * K + l * 4);
+    s.x += t.x;
+    s.y += t.y;
+    s.z += t.z;
+    s.w += t.w;
+  }
+  s = reduce_groups<W>(s);
+  if (g == 0) {
+    float4 o = *reinterpret_cast<float4*>(crow + l * 4);
+    o.x += s.x;
+    o.y += s.y;
+    o.z += s.z;
+    o.w += s.w;
+    *reinterpret_cast<float4*>(crow + l * 4) = o;
+  }
+}
+
 __global__ void __launch_bounds__(kBlockThreads)
 carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
                    const float* __restrict__ carry_val, float* __restrict__ C) {
@@ -556,25 +614,18 @@ carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
       break;
     }
     float* crow = C + (int64_t)hr * K;
-    if ((K & 3) == 0) {
+    const float* src = carry_val + first * K;
+    if (K == 32) {
+      add_carries_grouped<8>(src, len, K, crow, lane);
+    } else if (K == 64) {
+      add_carries_grouped<16>(src, len, K, crow, lane);
+    } else if (K == 128) {
+      add_carries_grouped<32>(src, len, K, crow, lane);
+    } else if ((K & 3) == 0) {
       for (int col = lane * 4; col < K; col += 128) {
-        const float* src = carry_val + first * K + col;
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        int64_t i = 0;
-        for (; i + 8 <= len; i += 8) {
-          float4 t[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) t[u] = *reinterpret_cast<const float4*>(src + (i + u) * K);
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            s.x += t[u].x;
-            s.y += t[u].y;
-            s.z += t[u].z;
-            s.w += t[u].w;
-          }
-        }
-        for (; i < len; ++i) {
-          const float4 t = *reinterpret_cast<const float4*>(src + i * K);
+        for (int64_t i = 0; i < len; ++i) {
+          const float4 t = *reinterpret_cast<const float4*>(src + i * K + col);
           s.x += t.x;
           s.y += t.y;
           s.z += t.z;
@@ -590,7 +641,7 @@ carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
     } else {
       for (int col = lane; col < K; col += 32) {
         float s = 0.f;
-        for (int64_t i = 0; i < len; ++i) s += carry_val[(first + i) * K + col];
+        for (int64_t i = 0; i < len; ++i) s += src[i * K + col];
         crow[col] += s;
       }
     }
@@ -715,24 +766,24 @@ int launch_balanced(hpspmm_ctx* ctx, bool hint, bool rowsplit, int M, int n_chun
   return HPSPMM_OK;
 }
 
-template <int W, int U, int MINB>
+template <int W, int U, int MINB, int BT = kBlockThreads>
 int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* row_ptr,
                 const int32_t* col_idx, const float* vals, const float* B, float* C,
                 const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
                 float* carry_val, cudaStream_t stream) {
-  const int chunks_per_block = kBlockThreads / 32;
+  const int chunks_per_block = BT / 32;
   const int n_chunk_blocks = (n_chunks + chunks_per_block - 1) / chunks_per_block;
-  int n_zero_blocks = (M + kBlockThreads - 1) / kBlockThreads;
-  const int cap = ctx->sm_count * 2;
+  int n_zero_blocks = (M + BT - 1) / BT;
+  const int cap = ctx->sm_count * 2 * (kBlockThreads / BT);
   if (n_zero_blocks > cap) n_zero_blocks = cap;
   const unsigned grid = (unsigned)(n_chunk_blocks + n_zero_blocks);
   if (grid == 0) return HPSPMM_OK;
   if (hint)
-    spmm_warp_kernel<W, U, MINB, true><<<grid, kBlockThreads, 0, stream>>>(
+    spmm_warp_kernel<W, U, MINB, true, BT><<<grid, BT, 0, stream>>>(
         M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
         carry_row, carry_val);
   else
-    spmm_warp_kernel<W, U, MINB, false><<<grid, kBlockThreads, 0, stream>>>(
+    spmm_warp_kernel<W, U, MINB, false, BT><<<grid, BT, 0, stream>>>(
         M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
         carry_row, carry_val);
   ctx->launches++;
@@ -830,32 +881,32 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
   if (K == 32) {
     if (rowsplit) st = launch_balanced<8, 1, 8, 4>(HPSPMM_ARGS);
     else switch (variant) {
-      case 1: st = launch_warp<8, 8, 4>(HPSPMM_WARGS); break;
+      case 1: st = launch_warp<8, 4, 5>(HPSPMM_WARGS); break;
       case 2: st = launch_warp<8, 4, 6>(HPSPMM_WARGS); break;
-      case 3: st = launch_warp<8, 8, 3>(HPSPMM_WARGS); break;
+      case 3: st = launch_warp<8, 4, 10, 128>(HPSPMM_WARGS); break;
       case 4: st = launch_warp<8, 4, 4>(HPSPMM_WARGS); break;
-      case 5: st = launch_warp<8, 2, 8>(HPSPMM_WARGS); break;
-      default: st = launch_warp<8, 4, 5>(HPSPMM_WARGS); break;
+      case 5: st = launch_warp<8, 4, 16, 64>(HPSPMM_WARGS); break;
+      default: st = launch_warp<8, 4, 20, 64>(HPSPMM_WARGS); break;
     }
   } else if (K == 64) {
     if (rowsplit) st = launch_balanced<16, 1, 8, 4>(HPSPMM_ARGS);
     else switch (variant) {
-      case 1: st = launch_warp<16, 8, 4>(HPSPMM_WARGS); break;
+      case 1: st = launch_warp<16, 4, 5>(HPSPMM_WARGS); break;
       case 2: st = launch_warp<16, 4, 6>(HPSPMM_WARGS); break;
-      case 3: st = launch_warp<16, 8, 3>(HPSPMM_WARGS); break;
+      case 3: st = launch_warp<16, 4, 10, 128>(HPSPMM_WARGS); break;
       case 4: st = launch_warp<16, 4, 4>(HPSPMM_WARGS); break;
-      case 5: st = launch_warp<16, 2, 8>(HPSPMM_WARGS); break;
-      default: st = launch_warp<16, 4, 5>(HPSPMM_WARGS); break;
+      case 5: st = launch_warp<16, 4, 16, 64>(HPSPMM_WARGS); break;
+      default: st = launch_warp<16, 4, 20, 64>(HPSPMM_WARGS); break;
     }
   } else if (K == 128) {
     if (rowsplit) st = launch_balanced<32, 1, 8, 4>(HPSPMM_ARGS);
     else switch (variant) {
-      case 1: st = launch_warp<32, 8, 4>(HPSPMM_WARGS); break;
+      case 1: st = launch_warp<32, 4, 5>(HPSPMM_WARGS); break;
       case 2: st = launch_warp<32, 4, 6>(HPSPMM_WARGS); break;
-      case 3: st = launch_warp<32, 8, 3>(HPSPMM_WARGS); break;
+      case 3: st = launch_warp<32, 4, 10, 128>(HPSPMM_WARGS); break;
       case 4: st = launch_warp<32, 4, 4>(HPSPMM_WARGS); break;
-      case 5: st = launch_warp<32, 2, 8>(HPSPMM_WARGS); break;
-      default: st = launch_warp<32, 4, 5>(HPSPMM_WARGS); break;
+      case 5: st = launch_warp<32, 4, 16, 64>(HPSPMM_WARGS); break;
+      default: st = launch_warp<32, 4, 20, 64>(HPSPMM_WARGS); break;
     }
   }
 #undef HPSPMM_ARGS
