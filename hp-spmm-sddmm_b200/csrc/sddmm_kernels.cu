@@ -1,11 +1,8 @@
 // FP32 SDDMM over a CSR pattern for sm_100a: out[j] = dot(X[row(j), :], Y[col[j], :]).
 //
 // The reference names SDDMM but ships no code for it (only the unused ResInfo::sddmm_*
-// fields, include/spmm/mm/spmm_common.h:130-135).  The kernel reuses the nnz-balanced
-// chunk table of the SpMM: a sub-warp of W = K/4 lanes owns one chunk, keeps its
-// fragment of the current row of X in registers, gathers fragments of rows of Y as
-// float4, and reduces U = 8 partial dot products across the sub-warp at once with a
-// transposing butterfly (7 shuffles for 8 results instead of 8 * log2(W)).
+// fields, include/spmm/mm/spmm_common.h:130-135).  The kernels reuse the nnz-balanced chunk
+// table of the SpMM (one warp per chunk); A's values are not multiplied in.
 #include "device_utils.cuh"
 #include "hpspmm_internal.h"
 
@@ -49,102 +46,145 @@ __device__ __forceinline__ void next_row(const int* __restrict__ row_ptr, int M,
   row_end = e;
 }
 
-// Sums p[0..7] over each group of 8 adjacent lanes; on return p[0] of lane l holds the
-// group total of the value whose index is the 3-bit reversal of (l & 7).
-__device__ __forceinline__ void reduce8_transposed(float (&p)[8], unsigned mask, int lane) {
+// ---- warp kernel: one warp per chunk, G = 32/W interleaved lane groups, K = 4 * W --------
+// Same shape as the SpMM warp kernel: (col) tiles of 32 entries staged in shared memory with
+// asynchronous copies; in every step group g takes entry G*s+g and gathers its float4 of that
+// row of Y, U = 4 steps at a time.  The fragment of the current row of X stays in registers;
+// row changes are warp-uniform.  The four partial dot products of a batch are reduced across
+// the W lanes of each group with a transposing butterfly (4 shuffles for 4 results at W = 8).
+
+// Sums p[0..3] over each group of 4 adjacent lanes; afterwards p[0] of lane l holds the total
+// of the value whose index is the 2-bit reversal of (l & 3).
+__device__ __forceinline__ void reduce4_transposed(float (&p)[4], int lane) {
   {
     const bool up = lane & 1;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float send = up ? p[i] : p[i + 4];
-      const float keep = up ? p[i + 4] : p[i];
-      p[i] = keep + __shfl_xor_sync(mask, send, 1);
-    }
-  }
-  {
-    const bool up = lane & 2;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const float send = up ? p[i] : p[i + 2];
       const float keep = up ? p[i + 2] : p[i];
-      p[i] = keep + __shfl_xor_sync(mask, send, 2);
+      p[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
     }
   }
   {
-    const bool up = lane & 4;
+    const bool up = lane & 2;
     const float send = up ? p[0] : p[1];
     const float keep = up ? p[1] : p[0];
-    p[0] = keep + __shfl_xor_sync(mask, send, 4);
+    p[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
   }
 }
 
-__device__ __forceinline__ int bitrev3(int x) { return ((x & 1) << 2) | (x & 2) | ((x >> 2) & 1); }
+template <int W, bool HINT, int BT>
+__global__ void __launch_bounds__(BT)
+sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
+                  const int* __restrict__ col_idx, const float* __restrict__ X,
+                  const float* __restrict__ Y, float* __restrict__ out,
+                  const int* __restrict__ chunk_start, const int* __restrict__ chunk_row) {
+  constexpr int K = 4 * W;
+  constexpr int G = 32 / W;
+  constexpr int T = 32;
+  constexpr int U = 4;
+  constexpr int BATCH = U * G;
+  constexpr int STAGES = 2;
+  static_assert(T % BATCH == 0, "batch must tile the staged tile");
+  __shared__ int tiles[BT / 32][STAGES][T];
 
-template <int W, int R, bool HINT>
-__global__ void __launch_bounds__(kBlockThreads)
-sddmm_balanced_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
-                      const int* __restrict__ col_idx, const float* __restrict__ X,
-                      const float* __restrict__ Y, float* __restrict__ out,
-                      const int* __restrict__ chunk_start, const int* __restrict__ chunk_row) {
-  constexpr int K = 4 * W * R;
-  constexpr int U = 8;
-  const int lane = threadIdx.x & (W - 1);
-  const int worker = (int)(((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) / W);
-  if (worker >= n_chunks) return;
-  const unsigned mask = subwarp_mask<W>();
-  const uint64_t policy = policy_evict_last();
+  const int lane = threadIdx.x & 31;
+  const int g = lane / W;
+  const int l = lane % W;
+  const int chunk = (int)(((int64_t)blockIdx.x * BT + threadIdx.x) >> 5);
+  if (chunk >= n_chunks) return;
+  const uint64_t policy = HINT ? policy_evict_last() : 0ull;
+  int(*my)[T] = tiles[threadIdx.x >> 5];
 
-  const int n0 = __ldg(chunk_start + worker);
-  const int n1 = __ldg(chunk_start + worker + 1);
-  int row = __ldg(chunk_row + worker);
+  const int n0 = __ldg(chunk_start + chunk);
+  const int n1 = __ldg(chunk_start + chunk + 1);
+  int row = __ldg(chunk_row + chunk);
   int row_end = __ldg(row_ptr + row + 1);
 
-  float4 x[R];
-  auto load_x = [&]() {
-    const float* xr = X + (int64_t)row * K + lane * 4;
-#pragma unroll
-    for (int r = 0; r < R; ++r) x[r] = __ldg(reinterpret_cast<const float4*>(xr + r * W * 4));
+  auto stage_tile = [&](int stage, int base) {
+    const int j = base + lane;
+    if (j < n1)
+      cp_async_4(&my[stage][lane], col_idx + j);
+    else
+      my[stage][lane] = 0;   // past the chunk: column 0 (a valid row of Y), result discarded
+    cp_async_commit();
   };
-  load_x();
-  const float* Yl = Y + lane * 4;
+  stage_tile(0, n0);
+  stage_tile(1, n0 + T);
 
-  for (int base = n0; base < n1; base += W) {
-    const int jj = base + lane;
-    int mycol = 0;
-    if (jj < n1) mycol = ld_stream(col_idx + jj);
+  float4 x = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row * K + l * 4));
+  const float* Yl = Y + l * 4;
+
+  // entry `next_entry` starts a later row: find it and fetch its fragment of X
+  auto next_x = [&](int next_entry) {
+    int e, probes = 0;
+    do {
+      ++row;
+      e = __ldg(row_ptr + row + 1);
+    } while (e <= next_entry && ++probes < 16);
+    if (e <= next_entry) {
+      int lo = row + 1, hi = M + 1;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(row_ptr + mid) <= next_entry)
+          lo = mid + 1;
+        else
+          hi = mid;
+      }
+      row = lo - 1;
+      e = __ldg(row_ptr + row + 1);
+    }
+    row_end = e;
+    x = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row * K + l * 4));
+  };
+
+  int stage = 0;
+  for (int base = n0; base < n1; base += T) {
+    cp_async_wait<STAGES - 1>();
+    __syncwarp();
+    const int* tile = &my[stage][g];
 #pragma unroll 1
-    for (int u0 = 0; u0 < W; u0 += U) {
+    for (int u0 = 0; u0 < T; u0 += BATCH) {
       const int j0 = base + u0;
       if (j0 >= n1) break;
-      const int cnt = min(U, n1 - j0);
-      float4 y[U][R];
+      float4 y[U];
 #pragma unroll
-      for (int i = 0; i < U; ++i) {
-        const int c = __shfl_sync(mask, mycol, u0 + i, W);  // lanes past n1 hold column 0
-        const float* p = Yl + (int64_t)c * K;
-#pragma unroll
-        for (int r = 0; r < R; ++r) y[i][r] = ld_gather<HINT>(p + r * W * 4, policy);
-      }
+      for (int i = 0; i < U; ++i) y[i] = ld_gather<HINT>(Yl + (int64_t)tile[u0 + i * G] * K, policy);
       float part[U];
+      if (row_end >= j0 + BATCH) {
 #pragma unroll
-      for (int i = 0; i < U; ++i) {
-        if (i < cnt && j0 + i >= row_end) {
-          next_row(row_ptr, M, j0 + i, row, row_end);
-          load_x();
+        for (int i = 0; i < U; ++i) part[i] = dot4(x, y[i], 0.f);
+      } else {
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+          const int lo = j0 + i * G;
+          const int hi = min(lo + G, n1);
+          const int mine = lo + g;
+          int cur = lo;
+          part[i] = 0.f;
+          while (row_end < hi) {   // warp-uniform: the current row ends inside this step
+            if (mine >= cur && mine < row_end) part[i] = dot4(x, y[i], 0.f);
+            cur = row_end;
+            next_x(cur);
+          }
+          if (mine >= cur) part[i] = dot4(x, y[i], 0.f);
         }
-        float s = 0.f;
-#pragma unroll
-        for (int r = 0; r < R; ++r) s = dot4(x[r], y[i][r], s);
-        part[i] = s;
       }
-      reduce8_transposed(part, mask, lane);
+      // reduce the U partial dot products over the W lanes of each group
+      reduce4_transposed(part, lane);
       float total = part[0];
-      if (W >= 16) total += __shfl_xor_sync(mask, total, 8);
-      if (W >= 32) total += __shfl_xor_sync(mask, total, 16);
-      const int slot = bitrev3(lane & 7);
-      if (lane < 8 && slot < cnt) out[j0 + slot] = total;
+      total += __shfl_xor_sync(0xffffffffu, total, 4);
+      if (W >= 16) total += __shfl_xor_sync(0xffffffffu, total, 8);
+      if (W >= 32) total += __shfl_xor_sync(0xffffffffu, total, 16);
+      const int slot = ((l & 1) << 1) | ((l >> 1) & 1);   // which of the U entries lane l holds
+      const int j = j0 + slot * G + g;
+      if (l < 4 && j < n1) out[j] = total;
     }
+    __syncwarp();
+    stage_tile(stage, base + STAGES * T);
+    stage ^= 1;
   }
+  cp_async_wait<0>();
 }
 
 // Any K: one warp per chunk, one entry at a time, lanes stride over the columns.
@@ -187,14 +227,16 @@ template <int W, int R>
 void launch_sddmm(bool hint, int M, int n_chunks, const int32_t* row_ptr, const int32_t* col_idx,
                   const float* X, const float* Y, float* out, const int32_t* chunk_start,
                   const int32_t* chunk_row, cudaStream_t s) {
-  const int wpb = kBlockThreads / W;
-  const unsigned grid = (unsigned)((n_chunks + wpb - 1) / wpb);
+  static_assert(R == 1, "the warp kernel keeps one float4 per lane");
+  constexpr int BT = 64;
+  const int cpb = BT / 32;
+  const unsigned grid = (unsigned)((n_chunks + cpb - 1) / cpb);
   if (hint)
-    sddmm_balanced_kernel<W, R, true><<<grid, kBlockThreads, 0, s>>>(
-        M, n_chunks, row_ptr, col_idx, X, Y, out, chunk_start, chunk_row);
+    sddmm_warp_kernel<W, true, BT><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
+                                                       chunk_start, chunk_row);
   else
-    sddmm_balanced_kernel<W, R, false><<<grid, kBlockThreads, 0, s>>>(
-        M, n_chunks, row_ptr, col_idx, X, Y, out, chunk_start, chunk_row);
+    sddmm_warp_kernel<W, false, BT><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
+                                                        chunk_start, chunk_row);
 }
 
 }  // namespace
