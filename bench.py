@@ -38,9 +38,9 @@ GRAPH_SEED = 2
 FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the K = 128 product kernel on
-# the N = 1 workload, from the ncu capture summarised in profiles/spmm_balanced_rmat20.md.
-# None until a capture exists.
-NCU_TRAFFIC_BYTES_K128 = None
+# the N = 1 workload, from the ncu capture summarised in profiles/spmm_warp_kernel_rmat20.md
+# (1612.8 MB read + 572.8 MB written; the same full-size workload, about 1 GB on the device).
+NCU_TRAFFIC_BYTES_K128 = 2185679360
 
 
 def load_peak():
@@ -322,7 +322,7 @@ def main():
     Kd = max(ks)
     alg_bytes = pkg.spmm_algorithmic_bytes(M_l, n_ref, Kd, nnz_l)
     achieved = alg_bytes / (per_k_ms[Kd] * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "spmm_balanced_kernel K=%d (+carry fix-up)" % Kd,
+    roofline = {"bound": "hbm", "kernel": "spmm_warp_kernel K=%d (+carry fix-up)" % Kd,
                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_K128 if (n_gpus == 1 and Kd == 128) else None,
                 "algorithmic_bytes": alg_bytes, "ms": per_k_ms[Kd],
