@@ -177,12 +177,22 @@ def main():
     ap.add_argument("--only-k", type=int, default=0, help="profiling aid: run a single K")
     args = ap.parse_args()
 
-    import __graft_entry__ as entry
-    pkg = entry.load_package()
-
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    # torchrun exports OMP_NUM_THREADS=1 to every rank; the host-side generator and the CPU
+    # baseline are OpenMP code, so give them the cores back before the libraries load
+    # (all of them for the reference arm, which only rank 0 runs; an equal share otherwise).
+    cores = os.cpu_count() or 1
+    threads = os.environ.get("HPSPMM_BENCH_THREADS")
+    if threads is None and (world > 1 or "OMP_NUM_THREADS" not in os.environ):
+        threads = str(cores if args.impl == "reference" else max(1, cores // max(world, 1)))
+    if threads is not None:
+        os.environ["OMP_NUM_THREADS"] = threads
+
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
 
     if args.impl == "reference":
         if rank == 0:

@@ -4,7 +4,8 @@ import numpy as np
 # Tolerances (BASELINE north_star: max relative error 1e-4, FP32 summation order only).
 REL_TOL = 1e-4          # elementwise, on well-conditioned elements, and normwise
 BACKWARD_TOL = 1e-5     # |got - ref| / sum|terms|, every element
-WELL_CONDITIONED = 1e-3  # an element is well conditioned if |ref| >= this * sum|terms|
+WELL_CONDITIONED = 1e-2  # an element is well conditioned if |ref| >= this * sum|terms| (condition number <= 100;
+# at 1000 plain FP32 rounding, 6e-8 per operation, already reaches 1e-4 relative)
 
 
 def check_against_f64(got, ref64, abs_sum, what=""):

@@ -22,7 +22,7 @@ def test_csr_paths_against_reference_outputs(gpu_ctx, pkg, oracle, name):
     _, abs_sum = oracle.spmm_f64(rp, ci, v, B)
     ref = z["C_gespmm"].astype(np.float64)
     assert np.max(np.abs(C - ref) / np.maximum(abs_sum, 1e-30)) <= 1e-5
-    well = (np.abs(ref) >= 1e-3 * abs_sum) & (abs_sum > 0)
+    well = (np.abs(ref) >= 1e-2 * abs_sum) & (abs_sum > 0)
     assert np.max(np.abs(C - ref)[well] / np.abs(ref)[well]) <= 1e-4
     assert np.max(np.abs(C - z["C_lbspmm_div200"]) / np.maximum(abs_sum, 1e-30)) <= 2e-5
 

@@ -1,0 +1,85 @@
+"""BASELINE's large configurations at full size, checked through size-independent properties.
+
+With B = ones every element of row r of C equals the sum of that row's values, whatever the
+graph size; sampled rows (the heaviest, the first, the last, rows behind the 2^31-element mark)
+are brought back and compared with float64 row sums.  Config 3 is also compared with the oracle.
+"""
+import numpy as np
+import pytest
+
+from helpers import check_against_f64
+
+pytestmark = pytest.mark.gpu
+
+
+def _rows_vs_rowsums(ctx, pkg, g, K, sample_rows, use_plan=True):
+    M, N, nnz = g["M"], g["N"], g["nnz"]
+    d_rp, d_ci, d_v = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"]), ctx.upload(g["vals"])
+    d_B = ctx.alloc((N, K), np.float32)
+    ctx.fill(d_B, N * K, 1.0)
+    d_C = ctx.alloc((M, K), np.float32)
+    ctx.fill(d_C, M * K, -5.0)                      # stale data must be overwritten everywhere
+    plan = ctx.plan_create(M, nnz, d_rp, K) if use_plan else None
+    ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_B, d_C, plan=plan)
+    ctx.stream_sync()
+    rp = g["row_ptr"].astype(np.int64)
+    v64 = g["vals"].astype(np.float64)
+    for r in sample_rows:
+        got = np.empty(K, dtype=np.float32)
+        ctx.memcpy_d2h(got, d_C.ptr + int(r) * K * 4)
+        ctx.stream_sync()
+        seg = v64[rp[r]:rp[r + 1]]
+        want, scale = seg.sum(), np.abs(seg).sum()
+        assert np.all(np.abs(got - want) <= 1e-5 * max(scale, 1e-30)), (r, got[:4], want)
+        if len(seg) == 0:
+            assert np.all(got == 0)
+    if plan:
+        ctx.plan_destroy(plan)
+    for b in (d_rp, d_ci, d_v, d_B, d_C):
+        b.free()
+
+
+def _sample(g, extra=()):
+    deg = np.diff(g["row_ptr"])
+    M = g["M"]
+    rows = {0, 1, M - 1, M - 2, M // 2, int(deg.argmax())}
+    rows.update(int(r) for r in np.argsort(deg)[-4:])            # heaviest rows
+    rows.update(int(r) for r in np.flatnonzero(deg == 0)[:3])    # empty rows
+    rows.update(int(r) for r in np.random.default_rng(0).integers(0, M, 40))
+    rows.update(extra)
+    return sorted(rows)
+
+
+def test_cfg3_erdos_renyi_full_size(gpu_ctx, pkg, oracle):
+    """Config 3: M = N = 2,450,000, Poisson(50) degrees, K = 64, against the oracle."""
+    ctx = gpu_ctx
+    g = pkg.gen_erdos_renyi(2_450_000, 2_450_000, 50.0, seed=3)
+    assert 121_000_000 < g["nnz"] < 124_000_000
+    _rows_vs_rowsums(ctx, pkg, g, 64, _sample(g))
+    K, M, N, nnz = 64, g["M"], g["N"], g["nnz"]
+    B = pkg.host_fill_uniform(N * K, 3, 64, -1.0, 1.0).reshape(N, K)
+    d_rp, d_ci, d_v, d_B = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"]), ctx.upload(g["vals"]), ctx.upload(B)
+    d_C = ctx.alloc((M, K), np.float32)
+    ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_B, d_C)
+    C = d_C.to_host()
+    ref, abs_sum = oracle.spmm_f64(g["row_ptr"], g["col_idx"], g["vals"], B)
+    check_against_f64(C, ref, abs_sum, "cfg3")
+    for b in (d_rp, d_ci, d_v, d_B, d_C):
+        b.free()
+
+
+def test_offsets_beyond_2_31_elements(gpu_ctx, pkg):
+    """N*K and M*K above 2^31 elements: the dense operands need 64-bit offsets."""
+    M = N = 17_500_000
+    g = pkg.gen_uniform_degree(M, N, 0, 6, seed=9, vals_kind=pkg.VALS_UPM1)
+    assert M * 128 > 2 ** 31
+    last = [M - 1 - i for i in range(0, 200, 7)]       # rows whose element offset exceeds 2^31
+    _rows_vs_rowsums(gpu_ctx, pkg, g, 128, _sample(g, last), use_plan=False)
+
+
+def test_cfg4_rmat_scale24_k128(gpu_ctx, pkg):
+    """Config 4: R-MAT scale 24 (about 263 M entries, max degree > 10^5), K = 128."""
+    g = pkg.gen_rmat(24, 16, seed=4)
+    deg = np.diff(g["row_ptr"])
+    assert g["M"] == 1 << 24 and g["nnz"] > 250_000_000 and deg.max() > 100_000
+    _rows_vs_rowsums(gpu_ctx, pkg, g, 128, _sample(g))
