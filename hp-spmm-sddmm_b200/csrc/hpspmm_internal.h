@@ -40,6 +40,7 @@ struct hpspmm_plan {
   int64_t max_K;
   int32_t* chunk_start;
   int32_t* chunk_row;
+  int32_t* chunk_order;  // chunk ids, most rows first: the order in which warps take chunks
   int32_t* carry_row;
   float* carry_val;
   size_t bytes;
@@ -93,6 +94,15 @@ int32_t hpspmm_default_chunk_nnz(int64_t K);
 int hpspmm_launch_chunk_table(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
                               int32_t chunk_nnz, int64_t n_chunks, int32_t* chunk_start,
                               int32_t* chunk_row, int* split_count, cudaStream_t stream);
+
+// Processing order of the chunks: chunk ids sorted by the number of rows a chunk touches,
+// most rows first (a stable 8-bit counting sort on the device).  Chunks full of short rows
+// take several times longer than chunks inside one heavy row; started last they leave the GPU
+// draining, started first they overlap with the cheap ones.  `scratch` needs
+// hpspmm_order_scratch_bytes(n_chunks) bytes.
+size_t hpspmm_order_scratch_bytes(int64_t n_chunks);
+int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t n_chunks, const int32_t* chunk_row,
+                                int32_t* order_out, void* scratch, cudaStream_t stream);
 
 // ---- counter-based PRNG shared by host and device --------------------------------------
 // splitmix64 finaliser over (seed, stream, index); 24 high bits -> [0, 1).

@@ -78,7 +78,8 @@ __global__ void __launch_bounds__(BT)
 sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
                   const int* __restrict__ col_idx, const float* __restrict__ X,
                   const float* __restrict__ Y, float* __restrict__ out,
-                  const int* __restrict__ chunk_start, const int* __restrict__ chunk_row) {
+                  const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
+                  const int* __restrict__ chunk_order) {
   constexpr int K = 4 * W;
   constexpr int G = 32 / W;
   constexpr int T = 32;
@@ -91,8 +92,9 @@ sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
   const int lane = threadIdx.x & 31;
   const int g = lane / W;
   const int l = lane % W;
-  const int chunk = (int)(((int64_t)blockIdx.x * BT + threadIdx.x) >> 5);
-  if (chunk >= n_chunks) return;
+  const int slot = (int)(((int64_t)blockIdx.x * BT + threadIdx.x) >> 5);
+  if (slot >= n_chunks) return;
+  const int chunk = chunk_order != nullptr ? __ldg(chunk_order + slot) : slot;
   const uint64_t policy = HINT ? policy_evict_last() : 0ull;
   int(*my)[T] = tiles[threadIdx.x >> 5];
 
@@ -226,17 +228,17 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 template <int W, int R>
 void launch_sddmm(bool hint, int M, int n_chunks, const int32_t* row_ptr, const int32_t* col_idx,
                   const float* X, const float* Y, float* out, const int32_t* chunk_start,
-                  const int32_t* chunk_row, cudaStream_t s) {
+                  const int32_t* chunk_row, const int32_t* chunk_order, cudaStream_t s) {
   static_assert(R == 1, "the warp kernel keeps one float4 per lane");
   constexpr int BT = 64;
   const int cpb = BT / 32;
   const unsigned grid = (unsigned)((n_chunks + cpb - 1) / cpb);
   if (hint)
     sddmm_warp_kernel<W, true, BT><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
-                                                       chunk_start, chunk_row);
+                                                       chunk_start, chunk_row, chunk_order);
   else
     sddmm_warp_kernel<W, false, BT><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
-                                                        chunk_start, chunk_row);
+                                                        chunk_start, chunk_row, chunk_order);
 }
 
 }  // namespace
@@ -265,34 +267,40 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
   const bool hint = hint_mode == 2 || (hint_mode == 0 && K >= 64);
   const int32_t* chunk_start;
   const int32_t* chunk_row;
+  const int32_t* chunk_order = nullptr;
   int64_t n_chunks;
   if (plan) {
     HPSPMM_REQUIRE(ctx, plan->M == M && plan->nnz == nnz, "plan built for another matrix");
     HPSPMM_REQUIRE(ctx, plan->device == ctx->device, "plan built on another device");
     chunk_start = plan->chunk_start;
     chunk_row = plan->chunk_row;
+    chunk_order = plan->chunk_order;
     n_chunks = plan->n_chunks;
   } else {
     int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
     S = (S + 31) / 32 * 32;
     n_chunks = (nnz + S - 1) / S;
     const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
-    int st = hpspmm_ensure_scratch(ctx, 2 * b_int);
+    int st = hpspmm_ensure_scratch(ctx, 3 * b_int + hpspmm_order_scratch_bytes(n_chunks));
     if (st != HPSPMM_OK) return st;
     int32_t* cs = (int32_t*)ctx->scratch;
     int32_t* cr = (int32_t*)((char*)ctx->scratch + b_int);
+    int32_t* co = (int32_t*)((char*)ctx->scratch + 2 * b_int);
     st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, cs, cr, nullptr, s);
+    if (st != HPSPMM_OK) return st;
+    st = hpspmm_order_chunks_by_cost(ctx, M, n_chunks, cr, co, (char*)ctx->scratch + 3 * b_int, s);
     if (st != HPSPMM_OK) return st;
     chunk_start = cs;
     chunk_row = cr;
+    chunk_order = co;
   }
   const int m = (int)M, nc = (int)n_chunks;
   if (K == 32) {
-    launch_sddmm<8, 1>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, s);
+    launch_sddmm<8, 1>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
   } else if (K == 64) {
-    launch_sddmm<16, 1>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, s);
+    launch_sddmm<16, 1>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
   } else if (K == 128) {
-    launch_sddmm<32, 1>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, s);
+    launch_sddmm<32, 1>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
   } else {
     const unsigned grid = (unsigned)((n_chunks + kBlockThreads / 32 - 1) / (kBlockThreads / 32));
     if ((K & 3) == 0)

@@ -18,7 +18,6 @@
 // atomics on this path).  Empty rows are zeroed by extra blocks at the end of the same grid.
 // HPSPMM_ALGO_ROW_SPLIT keeps the reference's GESpMM shape (one sub-warp per row, every row
 // summed in storage order), which reproduces the CPU oracle bit for bit.
-#include <cstdlib>
 #include <mutex>
 #include <new>
 
@@ -287,7 +286,8 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
                  const int* __restrict__ col_idx, const float* __restrict__ vals,
                  const float* __restrict__ B, float* __restrict__ C,
                  const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
-                 int* __restrict__ carry_row, float* __restrict__ carry_val) {
+                 int* __restrict__ carry_row, float* __restrict__ carry_val,
+                 const int* __restrict__ chunk_order) {
   constexpr int K = 4 * W;
   constexpr int G = 32 / W;      // lane groups = entries gathered per warp instruction
   constexpr int T = 32;          // entries per staged tile
@@ -303,8 +303,10 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   const int lane = threadIdx.x & 31;
   const int g = lane / W;   // group
   const int l = lane % W;   // position inside the group = float4 column
-  const int chunk = (int)(((int64_t)blockIdx.x * BT + threadIdx.x) >> 5);
-  if (chunk >= n_chunks) return;
+  const int slot = (int)(((int64_t)blockIdx.x * BT + threadIdx.x) >> 5);
+  if (slot >= n_chunks) return;
+  // warps take chunks in the plan's order (chunks with many rows first), not in matrix order
+  const int chunk = chunk_order != nullptr ? __ldg(chunk_order + slot) : slot;
   const uint64_t policy = HINT ? policy_evict_last() : 0ull;
   int2(*my)[T] = tiles[threadIdx.x >> 5];
 
@@ -436,15 +438,17 @@ spmm_generic_kernel(int M, int K, int n_chunks, int n_chunk_blocks, const int* _
                     const int* __restrict__ col_idx, const float* __restrict__ vals,
                     const float* __restrict__ B, float* __restrict__ C,
                     const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
-                    int* __restrict__ carry_row, float* __restrict__ carry_val) {
+                    int* __restrict__ carry_row, float* __restrict__ carry_val,
+                    const int* __restrict__ chunk_order) {
   if ((int)blockIdx.x >= n_chunk_blocks) {
     if (blockIdx.y == 0)
       zero_empty_rows(M, K, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks);
     return;
   }
   const int lane = threadIdx.x & 31;
-  const int worker = (int)(((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) >> 5);
-  if (worker >= n_chunks) return;
+  const int slot = (int)(((int64_t)blockIdx.x * kBlockThreads + threadIdx.x) >> 5);
+  if (slot >= n_chunks) return;
+  const int worker = (!ROWSPLIT && chunk_order != nullptr) ? __ldg(chunk_order + slot) : slot;
   const int kb = blockIdx.y * (32 * VEC * NS);
 
   int n0, n1, row, row_end;
@@ -770,7 +774,7 @@ template <int W, int U, int MINB, int BT = kBlockThreads>
 int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* row_ptr,
                 const int32_t* col_idx, const float* vals, const float* B, float* C,
                 const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
-                float* carry_val, cudaStream_t stream) {
+                float* carry_val, const int32_t* chunk_order, cudaStream_t stream) {
   const int chunks_per_block = BT / 32;
   const int n_chunk_blocks = (n_chunks + chunks_per_block - 1) / chunks_per_block;
   int n_zero_blocks = (M + BT - 1) / BT;
@@ -781,11 +785,11 @@ int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* 
   if (hint)
     spmm_warp_kernel<W, U, MINB, true, BT><<<grid, BT, 0, stream>>>(
         M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
-        carry_row, carry_val);
+        carry_row, carry_val, chunk_order);
   else
     spmm_warp_kernel<W, U, MINB, false, BT><<<grid, BT, 0, stream>>>(
         M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
-        carry_row, carry_val);
+        carry_row, carry_val, chunk_order);
   ctx->launches++;
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;
@@ -795,7 +799,8 @@ template <int VEC>
 int launch_generic(hpspmm_ctx* ctx, bool rowsplit, int M, int K, int n_chunks,
                    const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
                    const float* B, float* C, const int32_t* chunk_start, const int32_t* chunk_row,
-                   int32_t* carry_row, float* carry_val, cudaStream_t stream) {
+                   int32_t* carry_row, float* carry_val, const int32_t* chunk_order,
+                   cudaStream_t stream) {
   constexpr int NS = 4;
   const int kblock = 32 * VEC * NS;
   const int n_kblocks = (K + kblock - 1) / kblock;
@@ -812,11 +817,11 @@ int launch_generic(hpspmm_ctx* ctx, bool rowsplit, int M, int K, int n_chunks,
   if (rowsplit)
     spmm_generic_kernel<VEC, NS, true><<<grid, kBlockThreads, 0, stream>>>(
         M, K, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
-        carry_row, carry_val);
+        carry_row, carry_val, nullptr);
   else
     spmm_generic_kernel<VEC, NS, false><<<grid, kBlockThreads, 0, stream>>>(
         M, K, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
-        carry_row, carry_val);
+        carry_row, carry_val, chunk_order);
   ctx->launches++;
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;
@@ -868,55 +873,29 @@ int check_spmm_args(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nn
 int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, int64_t n_chunks,
              const int32_t* row_ptr, const int32_t* col_idx, const float* vals, const float* B,
              float* C, const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
-             float* carry_val, bool need_fixup, cudaStream_t stream) {
+             float* carry_val, const int32_t* chunk_order, bool need_fixup, cudaStream_t stream) {
   int st;
   const int m = (int)M, nc = (int)n_chunks;
+  // Tuning on B200 (R-MAT scale 20): 64-thread blocks, U = 4 gather steps in flight per lane and
+  // at most 51 registers (20 blocks per SM) beat 128/256-thread blocks, U = 2/8/16 and the
+  // 32/40/64/80-register builds at every K.
 #define HPSPMM_ARGS ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, stream
-#define HPSPMM_WARGS ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, stream
-  static int variant = -1;
-  if (variant < 0) {
-    const char* e = getenv("HPSPMM_VARIANT");
-    variant = e ? atoi(e) : 0;
-  }
+#define HPSPMM_WARGS ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, chunk_order, stream
   if (K == 32) {
-    if (rowsplit) st = launch_balanced<8, 1, 8, 4>(HPSPMM_ARGS);
-    else switch (variant) {
-      case 1: st = launch_warp<8, 4, 5>(HPSPMM_WARGS); break;
-      case 2: st = launch_warp<8, 4, 6>(HPSPMM_WARGS); break;
-      case 3: st = launch_warp<8, 4, 10, 128>(HPSPMM_WARGS); break;
-      case 4: st = launch_warp<8, 4, 4>(HPSPMM_WARGS); break;
-      case 5: st = launch_warp<8, 4, 16, 64>(HPSPMM_WARGS); break;
-      default: st = launch_warp<8, 4, 20, 64>(HPSPMM_WARGS); break;
-    }
+    st = rowsplit ? launch_balanced<8, 1, 8, 4>(HPSPMM_ARGS) : launch_warp<8, 4, 20, 64>(HPSPMM_WARGS);
   } else if (K == 64) {
-    if (rowsplit) st = launch_balanced<16, 1, 8, 4>(HPSPMM_ARGS);
-    else switch (variant) {
-      case 1: st = launch_warp<16, 4, 5>(HPSPMM_WARGS); break;
-      case 2: st = launch_warp<16, 4, 6>(HPSPMM_WARGS); break;
-      case 3: st = launch_warp<16, 4, 10, 128>(HPSPMM_WARGS); break;
-      case 4: st = launch_warp<16, 4, 4>(HPSPMM_WARGS); break;
-      case 5: st = launch_warp<16, 4, 16, 64>(HPSPMM_WARGS); break;
-      default: st = launch_warp<16, 4, 20, 64>(HPSPMM_WARGS); break;
-    }
+    st = rowsplit ? launch_balanced<16, 1, 8, 4>(HPSPMM_ARGS) : launch_warp<16, 4, 20, 64>(HPSPMM_WARGS);
   } else if (K == 128) {
-    if (rowsplit) st = launch_balanced<32, 1, 8, 4>(HPSPMM_ARGS);
-    else switch (variant) {
-      case 1: st = launch_warp<32, 4, 5>(HPSPMM_WARGS); break;
-      case 2: st = launch_warp<32, 4, 6>(HPSPMM_WARGS); break;
-      case 3: st = launch_warp<32, 4, 10, 128>(HPSPMM_WARGS); break;
-      case 4: st = launch_warp<32, 4, 4>(HPSPMM_WARGS); break;
-      case 5: st = launch_warp<32, 4, 16, 64>(HPSPMM_WARGS); break;
-      default: st = launch_warp<32, 4, 20, 64>(HPSPMM_WARGS); break;
-    }
+    st = rowsplit ? launch_balanced<32, 1, 8, 4>(HPSPMM_ARGS) : launch_warp<32, 4, 20, 64>(HPSPMM_WARGS);
   }
 #undef HPSPMM_ARGS
 #undef HPSPMM_WARGS
   else if ((K & 3) == 0)
     st = launch_generic<4>(ctx, rowsplit, m, (int)K, nc, row_ptr, col_idx, vals, B, C, chunk_start,
-                           chunk_row, carry_row, carry_val, stream);
+                           chunk_row, carry_row, carry_val, chunk_order, stream);
   else
     st = launch_generic<1>(ctx, rowsplit, m, (int)K, nc, row_ptr, col_idx, vals, B, C, chunk_start,
-                           chunk_row, carry_row, carry_val, stream);
+                           chunk_row, carry_row, carry_val, chunk_order, stream);
   if (st != HPSPMM_OK) return st;
   if (!rowsplit && need_fixup && n_chunks > 0) {
     const unsigned blocks = (unsigned)((n_chunks + kBlockThreads - 1) / kBlockThreads);
@@ -955,7 +934,9 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* r
   const size_t b_row = align_up((size_t)(p->n_chunks + 1) * 4, 256);
   const size_t b_crow = align_up((size_t)(p->n_chunks + 1) * 4, 256);
   const size_t b_cval = align_up((size_t)(p->n_chunks + 1) * (size_t)max_K * 4, 256);
-  p->bytes = b_start + b_row + b_crow + b_cval;
+  const size_t b_order = align_up((size_t)(p->n_chunks + 1) * 4, 256);
+  const size_t b_sort = hpspmm_order_scratch_bytes(p->n_chunks);   // only needed while building
+  p->bytes = b_start + b_row + b_crow + b_cval + b_order + b_sort;
   char* base = nullptr;
   cudaError_t e = cudaMalloc((void**)&base, p->bytes);
   if (e != cudaSuccess) {
@@ -966,6 +947,8 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* r
   p->chunk_row = (int32_t*)(base + b_start);
   p->carry_row = (int32_t*)(base + b_start + b_row);
   p->carry_val = (float*)(base + b_start + b_row + b_crow);
+  p->chunk_order = (int32_t*)(base + b_start + b_row + b_crow + b_cval);
+  void* sort_scratch = base + b_start + b_row + b_crow + b_cval + b_order;
   cudaStream_t s = (cudaStream_t)stream;
   int st = HPSPMM_OK;
   int split = 0;
@@ -973,6 +956,8 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* r
   if (e == cudaSuccess && M > 0)
     st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, p->n_chunks, p->chunk_start,
                                    p->chunk_row, ctx->flag, s);
+  if (e == cudaSuccess && st == HPSPMM_OK && M > 0)
+    st = hpspmm_order_chunks_by_cost(ctx, M, p->n_chunks, p->chunk_row, p->chunk_order, sort_scratch, s);
   if (e == cudaSuccess && st == HPSPMM_OK)
     e = cudaMemcpyAsync(&split, ctx->flag, sizeof(int), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess && st == HPSPMM_OK) e = cudaStreamSynchronize(s);
@@ -1019,7 +1004,7 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
   const int algo = opts ? opts->algo : HPSPMM_ALGO_AUTO;
   if (algo == HPSPMM_ALGO_ROW_SPLIT) {
     return run_spmm(ctx, hint, true, M, K, M, row_ptr, col_idx, vals, B, C, nullptr, nullptr,
-                    nullptr, nullptr, false, s);
+                    nullptr, nullptr, nullptr, false, s);
   }
   HPSPMM_REQUIRE(ctx, algo == HPSPMM_ALGO_AUTO || algo == HPSPMM_ALGO_BALANCED, "unknown algo");
   if (plan) {
@@ -1028,25 +1013,30 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
     HPSPMM_REQUIRE(ctx, plan->device == ctx->device, "plan built on another device");
     return run_spmm(ctx, hint, false, M, K, plan->n_chunks, row_ptr, col_idx, vals, B, C,
                     plan->chunk_start, plan->chunk_row, plan->carry_row, plan->carry_val,
-                    plan->n_split_chunks > 0, s);
+                    plan->chunk_order, plan->n_split_chunks > 0, s);
   }
   int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
   S = (S + 31) / 32 * 32;
   const int64_t n_chunks = (nnz + S - 1) / S;
   const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
   const size_t b_cval = align_up((size_t)(n_chunks + 1) * (size_t)K * 4, 256);
-  st = hpspmm_ensure_scratch(ctx, 3 * b_int + b_cval);
+  const size_t b_sort = hpspmm_order_scratch_bytes(n_chunks);
+  st = hpspmm_ensure_scratch(ctx, 4 * b_int + b_cval + b_sort);
   if (st != HPSPMM_OK) return st;
   char* base = (char*)ctx->scratch;
   int32_t* chunk_start = (int32_t*)base;
   int32_t* chunk_row = (int32_t*)(base + b_int);
   int32_t* carry_row = (int32_t*)(base + 2 * b_int);
-  float* carry_val = (float*)(base + 3 * b_int);
+  int32_t* chunk_order = (int32_t*)(base + 3 * b_int);
+  float* carry_val = (float*)(base + 4 * b_int);
+  void* sort_scratch = base + 4 * b_int + b_cval;
   st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, chunk_start, chunk_row,
                                  nullptr, s);
   if (st != HPSPMM_OK) return st;
+  st = hpspmm_order_chunks_by_cost(ctx, M, n_chunks, chunk_row, chunk_order, sort_scratch, s);
+  if (st != HPSPMM_OK) return st;
   return run_spmm(ctx, hint, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
-                  chunk_row, carry_row, carry_val, true, s);
+                  chunk_row, carry_row, carry_val, chunk_order, true, s);
 }
 
 int hpspmm_spmm_csr_f32_host(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz,
@@ -1236,7 +1226,7 @@ extern "C" int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M,
                                  nullptr, s);
   if (st == HPSPMM_OK)
     st = run_spmm(&local, K >= 64, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
-                  chunk_row, carry_row, carry_val, true, s);
+                  chunk_row, carry_row, carry_val, /*chunk_order=*/nullptr, true, s);
   if (st != HPSPMM_OK) write_err(err_buf, err_len, local.err);
   return st;
 }
