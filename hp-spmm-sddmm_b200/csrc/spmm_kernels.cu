@@ -832,9 +832,11 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 }  // namespace
 
 int32_t hpspmm_default_chunk_nnz(int64_t K) {
-  // measured on B200 (R-MAT scale 20): 128 beats 64, 256 and 512 at K = 32, 64 and 128
-  (void)K;
-  return 128;
+  // measured on B200 (R-MAT scale 20, cost-ordered chunks): the best nominal chunk grows with
+  // the row width -- 128 entries at K = 32, 160 at K = 64, 256 at K = 128
+  if (K <= 32) return 128;
+  if (K <= 64) return 160;
+  return 256;
 }
 
 int hpspmm_launch_chunk_table(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
@@ -957,7 +959,8 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* r
     st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, p->n_chunks, p->chunk_start,
                                    p->chunk_row, ctx->flag, s);
   if (e == cudaSuccess && st == HPSPMM_OK && M > 0)
-    st = hpspmm_order_chunks_by_cost(ctx, M, p->n_chunks, p->chunk_row, p->chunk_order, sort_scratch, s);
+    st = hpspmm_order_chunks_by_cost(ctx, M, p->n_chunks, p->chunk_start, p->chunk_row, p->chunk_order,
+                                     sort_scratch, s);
   if (e == cudaSuccess && st == HPSPMM_OK)
     e = cudaMemcpyAsync(&split, ctx->flag, sizeof(int), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess && st == HPSPMM_OK) e = cudaStreamSynchronize(s);
@@ -1033,7 +1036,7 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
   st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, chunk_start, chunk_row,
                                  nullptr, s);
   if (st != HPSPMM_OK) return st;
-  st = hpspmm_order_chunks_by_cost(ctx, M, n_chunks, chunk_row, chunk_order, sort_scratch, s);
+  st = hpspmm_order_chunks_by_cost(ctx, M, n_chunks, chunk_start, chunk_row, chunk_order, sort_scratch, s);
   if (st != HPSPMM_OK) return st;
   return run_spmm(ctx, hint, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
                   chunk_row, carry_row, carry_val, chunk_order, true, s);

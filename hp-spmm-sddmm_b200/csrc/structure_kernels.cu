@@ -249,14 +249,20 @@ __global__ void transposed_gather_kernel(int M, int64_t nnz, const int* __restri
   }
 }
 
-// key[c] = 255 - min(255, rows touched by chunk c): ascending keys = most rows first
-__global__ void chunk_cost_key_kernel(int M, int64_t n_chunks, const int* __restrict__ chunk_row,
-                                      int* __restrict__ keys) {
+// Cost estimate of chunk c in arbitrary units: entries / 8 (gather batches) + rows / 2 (each
+// row end costs a cross-group reduction, a store and a step along row_ptr), capped at 255.
+// key = 255 - cost, so ascending keys put the most expensive chunks first.
+__global__ void chunk_cost_key_kernel(int M, int64_t n_chunks, const int* __restrict__ chunk_start,
+                                      const int* __restrict__ chunk_row, int* __restrict__ keys) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += stride) {
     const int next = c + 1 < n_chunks ? chunk_row[c + 1] : M;
-    const int rows = next - chunk_row[c];
-    keys[c] = 255 - (rows < 0 ? 0 : (rows > 255 ? 255 : rows));
+    int rows = next - chunk_row[c];
+    rows = rows < 0 ? 0 : rows;
+    const int entries = chunk_start[c + 1] - chunk_start[c];
+    int cost = (entries >> 3) + (rows >> 1);
+    cost = cost > 255 ? 255 : cost;
+    keys[c] = 255 - cost;
   }
 }
 
@@ -279,8 +285,9 @@ size_t hpspmm_order_scratch_bytes(int64_t n_chunks) {
          align_up((size_t)scan_blocks * 4, 256);
 }
 
-int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t n_chunks, const int32_t* chunk_row,
-                                int32_t* order_out, void* scratch, cudaStream_t stream) {
+int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t n_chunks, const int32_t* chunk_start,
+                                const int32_t* chunk_row, int32_t* order_out, void* scratch,
+                                cudaStream_t stream) {
   if (n_chunks <= 0) return HPSPMM_OK;
   const int n_tiles = (int)((n_chunks + kTile - 1) / kTile);
   const int64_t hist_n = (int64_t)256 * n_tiles;
@@ -291,7 +298,8 @@ int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t n_chunks, co
   int* keys_sorted = (int*)(base + b_arr);
   int* hist = (int*)(base + 2 * b_arr);
   int* totals = (int*)(base + 2 * b_arr + align_up((size_t)hist_n * 4, 256));
-  chunk_cost_key_kernel<<<grid_for(ctx, n_chunks), kThreads, 0, stream>>>((int)M, n_chunks, chunk_row, keys);
+  chunk_cost_key_kernel<<<grid_for(ctx, n_chunks), kThreads, 0, stream>>>((int)M, n_chunks, chunk_start,
+                                                                          chunk_row, keys);
   radix_hist_kernel<<<n_tiles, kThreads, 0, stream>>>(keys, n_chunks, 0, n_tiles, hist);
   scan_block_totals_kernel<<<(unsigned)scan_blocks, kThreads, 0, stream>>>(hist, hist_n, totals);
   scan_single_block_kernel<<<1, kThreads, 0, stream>>>(totals, scan_blocks);
