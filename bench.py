@@ -175,6 +175,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--only-k", type=int, default=0, help="profiling aid: run a single K")
+    ap.add_argument("--b-sharded", action="store_true",
+                    help="B is produced row-sharded (a GNN layer's output): every step all-gathers it "
+                         "with NCCL into each GPU's own HBM before the local product")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -237,10 +240,18 @@ def main():
     plans = {K: ctx.plan_create(M_l, nnz_l, t_rp.data_ptr(), K, None, sptr) for K in ks}
     plan_info = {str(K): ctx.plan_info(plans[K]) for K in ks}
 
-    def step(events=None):
+    # --b-sharded: each rank owns N / world rows of B; the gathered copy is what the kernel reads
+    b_sharded = args.b_sharded and n_gpus > 1 and N % n_gpus == 0
+    if b_sharded:
+        rows_b = N // n_gpus
+        B_own = {K: Bs[K][rank * rows_b:(rank + 1) * rows_b].clone() for K in ks}
+
+    def step(events=None, collective=True):
         for i, K in enumerate(ks):
             if events is not None:
                 events[i][0].record(stream)
+            if b_sharded and collective:
+                dist.all_gather_into_tensor(Bs[K], B_own[K])
             ctx.spmm_csr(M_l, N, K, nnz_l, t_rp.data_ptr(), t_ci.data_ptr(), t_v.data_ptr(),
                          Bs[K].data_ptr(), Cs[K].data_ptr(), plan=plans[K], stream=sptr)
             if events is not None:
@@ -276,7 +287,7 @@ def main():
     if rank == 0:
         t_end = time.time() + 0.5
         while time.time() < t_end:
-            step()
+            step(collective=False)   # rank 0 alone: no collective here
         torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
 
@@ -375,6 +386,7 @@ def main():
                        "M": info["M"], "N": N, "nnz": info["nnz"], "max_degree": info["max_degree"],
                        "empty_rows": info["empty_rows"], "n_ref_rank0": n_ref,
                        "plan": plan_info, "l2": "operands larger than L2 (no flush)",
+                       "b": "all-gathered per step (NCCL)" if b_sharded else "replicated",
                        "parallelism": "row-shard x%d" % n_gpus},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks,

@@ -83,3 +83,42 @@ def test_cfg4_rmat_scale24_k128(gpu_ctx, pkg):
     deg = np.diff(g["row_ptr"])
     assert g["M"] == 1 << 24 and g["nnz"] > 250_000_000 and deg.max() > 100_000
     _rows_vs_rowsums(gpu_ctx, pkg, g, 128, _sample(g))
+
+
+def test_cfg5_gnn_layer_full_size(gpu_ctx, pkg, oracle):
+    """Config 5 on the config-2 graph at K = 64: forward C = A H, SDDMM dA = pattern(A) .* (dC H^T),
+    backward dH = A^T dC through the transposed CSR built on the device; one plan reused."""
+    ctx = gpu_ctx
+    K = 64
+    g = pkg.gen_rmat(20, 16, seed=2)
+    M, N, nnz = g["M"], g["N"], g["nnz"]
+    H = pkg.host_fill_uniform(N * K, 5, 1, -1.0, 1.0).reshape(N, K)
+    dC = pkg.host_fill_uniform(M * K, 5, 2, -1.0, 1.0).reshape(M, K)
+    d_rp, d_ci, d_v = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"]), ctx.upload(g["vals"])
+    d_H, d_dC = ctx.upload(H), ctx.upload(dC)
+    d_C = ctx.alloc((M, K), np.float32)
+    d_dA = ctx.alloc((nnz,), np.float32)
+    plan = ctx.plan_create(M, nnz, d_rp, K)
+    # forward
+    ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_H, d_C, plan=plan)
+    ref, abs_sum = oracle.spmm_f64(g["row_ptr"], g["col_idx"], g["vals"], H)
+    check_against_f64(d_C.to_host(), ref, abs_sum, "cfg5 forward")
+    # SDDMM over the pattern
+    ctx.sddmm_csr(M, N, K, nnz, d_rp, d_ci, d_dC, d_H, d_dA, plan=plan)
+    ref, abs_sum = oracle.sddmm_f64(g["row_ptr"], g["col_idx"], dC, H)
+    check_against_f64(d_dA.to_host(), ref, abs_sum, "cfg5 sddmm")
+    # backward through the device transpose
+    d_rpt, d_cit, d_vt = ctx.alloc((N + 1,), np.int32), ctx.alloc((nnz,), np.int32), ctx.alloc((nnz,), np.float32)
+    ctx.csr_transpose(M, N, nnz, d_rp, d_ci, d_v, d_rpt, d_cit, d_vt)
+    rpt, cit, vt, _ = oracle.csr_transpose(M, N, g["row_ptr"], g["col_idx"], g["vals"])
+    assert np.array_equal(d_rpt.to_host(), rpt) and np.array_equal(d_cit.to_host(), cit)
+    assert np.array_equal(d_vt.to_host(), vt)
+    d_dH = ctx.alloc((N, K), np.float32)
+    plan_t = ctx.plan_create(N, nnz, d_rpt, K)
+    ctx.spmm_csr(N, M, K, nnz, d_rpt, d_cit, d_vt, d_dC, d_dH, plan=plan_t)
+    ref, abs_sum = oracle.spmm_f64(rpt, cit, vt, dC)
+    check_against_f64(d_dH.to_host(), ref, abs_sum, "cfg5 backward")
+    ctx.plan_destroy(plan)
+    ctx.plan_destroy(plan_t)
+    for b in (d_rp, d_ci, d_v, d_H, d_dC, d_C, d_dA, d_rpt, d_cit, d_vt, d_dH):
+        b.free()
