@@ -90,21 +90,21 @@ inline CSR_Matrix get_csr_mat_from_smtx(const std::string& filename, long long& 
   return m;
 }
 
-// BASELINE config 1: per-row degree uniform in [deg_lo, deg_hi], values U(-1,1)
+// small benchmark configuration: per-row degree uniform in [deg_lo, deg_hi], values U(-1,1)
 inline CSR_Matrix gen_csr_uniform_degree(int64_t M, int64_t N, int deg_lo, int deg_hi, uint64_t seed) {
   hpspmm_graph* g = nullptr;
   const int st = hpspmm_gen_uniform_degree(M, N, deg_lo, deg_hi, seed, HPSPMM_VALS_UPM1, &g);
   if (st != HPSPMM_OK) throw hpspmm::Error(st, "hpspmm_gen_uniform_degree");
   return hpspmm::csr_from_graph(g);
 }
-// BASELINE config 3: Poisson(mean_degree) degrees, values U(0,1)
+// uniform sparse configuration: Poisson(mean_degree) degrees, values U(0,1)
 inline CSR_Matrix gen_csr_erdos_renyi(int64_t M, int64_t N, double mean_degree, uint64_t seed) {
   hpspmm_graph* g = nullptr;
   const int st = hpspmm_gen_erdos_renyi(M, N, mean_degree, seed, HPSPMM_VALS_U01, &g);
   if (st != HPSPMM_OK) throw hpspmm::Error(st, "hpspmm_gen_erdos_renyi");
   return hpspmm::csr_from_graph(g);
 }
-// BASELINE configs 2 and 4: symmetric R-MAT (0.57, 0.19, 0.19, 0.05), values U(0,1)
+// power-law configurations: symmetric R-MAT (0.57, 0.19, 0.19, 0.05), values U(0,1)
 inline CSR_Matrix gen_csr_rmat(int scale, int edge_factor, uint64_t seed) {
   hpspmm_graph* g = nullptr;
   const int st = hpspmm_gen_rmat(scale, edge_factor, 0.57, 0.19, 0.19, seed, HPSPMM_VALS_U01, &g);

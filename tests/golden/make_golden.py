@@ -77,7 +77,7 @@ def main():
                          "gespmm_equals_fp32_oracle": bool(np.array_equal(
                              C_ge, oracle_lib.spmm_f32(g["row_ptr"], g["col_idx"], g["vals"], B)))}
 
-    # BASELINE config 1 at full size: inputs are regenerated from their seeds by the test;
+    # The small uniform-degree benchmark configuration (4096 x 4096, K = 32) at full size: inputs are regenerated from their seeds by the test;
     # 64 sampled rows of the reference's output are stored.
     g = pkg.gen_uniform_degree(4096, 4096, 1, 32, seed=1, vals_kind=pkg.VALS_UPM1)
     B = pkg.host_fill_uniform(4096 * 32, 1, 10, -1.0, 1.0).reshape(4096, 32)

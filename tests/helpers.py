@@ -1,7 +1,7 @@
 """Shared helpers for the parity tests: error metrics and device round trips via the C ABI."""
 import numpy as np
 
-# Tolerances (BASELINE north_star: max relative error 1e-4, FP32 summation order only).
+# Tolerances (required: max relative error 1e-4, FP32 summation-order differences only).
 REL_TOL = 1e-4          # elementwise, on well-conditioned elements, and normwise
 BACKWARD_TOL = 1e-5     # |got - ref| / sum|terms|, every element
 WELL_CONDITIONED = 1e-2  # an element is well conditioned if |ref| >= this * sum|terms| (condition number <= 100;

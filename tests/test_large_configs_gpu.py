@@ -1,8 +1,8 @@
-"""BASELINE's large configurations at full size, checked through size-independent properties.
+"""The large benchmark configurations at full size, checked through size-independent properties.
 
 With B = ones every element of row r of C equals the sum of that row's values, whatever the
 graph size; sampled rows (the heaviest, the first, the last, rows behind the 2^31-element mark)
-are brought back and compared with float64 row sums.  Config 3 is also compared with the oracle.
+are brought back and compared with float64 row sums.  The uniform sparse case is also compared with the oracle.
 """
 import numpy as np
 import pytest
@@ -51,7 +51,7 @@ def _sample(g, extra=()):
 
 
 def test_cfg3_erdos_renyi_full_size(gpu_ctx, pkg, oracle):
-    """Config 3: M = N = 2,450,000, Poisson(50) degrees, K = 64, against the oracle."""
+    """Uniform sparse case: M = N = 2,450,000, Poisson(50) degrees, K = 64, against the oracle."""
     ctx = gpu_ctx
     g = pkg.gen_erdos_renyi(2_450_000, 2_450_000, 50.0, seed=3)
     assert 121_000_000 < g["nnz"] < 124_000_000
@@ -78,7 +78,7 @@ def test_offsets_beyond_2_31_elements(gpu_ctx, pkg):
 
 
 def test_cfg4_rmat_scale24_k128(gpu_ctx, pkg):
-    """Config 4: R-MAT scale 24 (about 263 M entries, max degree > 10^5), K = 128."""
+    """Large skewed case: R-MAT scale 24 (about 263 M entries, max degree > 10^5), K = 128."""
     g = pkg.gen_rmat(24, 16, seed=4)
     deg = np.diff(g["row_ptr"])
     assert g["M"] == 1 << 24 and g["nnz"] > 250_000_000 and deg.max() > 100_000
@@ -86,7 +86,7 @@ def test_cfg4_rmat_scale24_k128(gpu_ctx, pkg):
 
 
 def test_cfg5_gnn_layer_full_size(gpu_ctx, pkg, oracle):
-    """Config 5 on the config-2 graph at K = 64: forward C = A H, SDDMM dA = pattern(A) .* (dC H^T),
+    """A GNN layer on the R-MAT scale-20 graph at K = 64: forward C = A H, SDDMM dA = pattern(A) .* (dC H^T),
     backward dH = A^T dC through the transposed CSR built on the device; one plan reused."""
     ctx = gpu_ctx
     K = 64

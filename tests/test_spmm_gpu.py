@@ -15,7 +15,7 @@ def _check(ctx, pkg, oracle, row_ptr, col_idx, vals, B, what, **kw):
 
 
 def test_cfg1_small_csr(gpu_ctx, pkg, oracle):
-    """BASELINE config 1: M=N=4096, degree U{1..32}, K=32, values and B in U(-1,1)."""
+    """Small uniform-degree configuration: M=N=4096, degree U{1..32}, K=32, values and B in U(-1,1)."""
     g = pkg.gen_uniform_degree(4096, 4096, 1, 32, seed=1, vals_kind=pkg.VALS_UPM1)
     B = pkg.host_fill_uniform(4096 * 32, 1, 10, -1.0, 1.0).reshape(4096, 32)
     C, _ = _check(gpu_ctx, pkg, oracle, g["row_ptr"], g["col_idx"], g["vals"], B, "cfg1")
@@ -132,7 +132,7 @@ def test_overwrites_stale_output_and_linearity(gpu_ctx, pkg, oracle):
 
 
 def test_full_size_cfg2_k32(gpu_ctx, pkg, oracle):
-    """BASELINE config 2 at full size, K=32, against the oracle and by the row-sum property."""
+    """The power-law benchmark graph (R-MAT scale 20) at full size, K=32, against the oracle and by the row-sum property."""
     g = pkg.gen_rmat(20, 16, seed=2)
     K = 32
     B = pkg.host_fill_uniform(g["N"] * K, 2, 32, -1.0, 1.0).reshape(g["N"], K)
