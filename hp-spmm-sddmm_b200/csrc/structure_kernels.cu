@@ -236,15 +236,17 @@ __global__ void transposed_row_ptr_kernel(const int* __restrict__ sorted_keys, i
   }
 }
 
-__global__ void transposed_gather_kernel(int M, int64_t nnz, const int* __restrict__ row_ptr,
+// col_idx_t[t] = source row of transposed entry t, looked up in the expanded row-index array
+// (one random 4-byte read instead of a binary search over row_ptr per entry)
+__global__ void transposed_gather_kernel(int64_t nnz, const int* __restrict__ row_of,
                                          const float* __restrict__ vals, const int* __restrict__ perm,
                                          int* __restrict__ col_idx_t, float* __restrict__ vals_t,
                                          int* __restrict__ perm_out) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nnz; t += stride) {
     const int j = perm[t];
-    col_idx_t[t] = row_of_entry(row_ptr, M, j);
-    if (vals_t) vals_t[t] = vals[j];
+    col_idx_t[t] = __ldg(row_of + j);
+    if (vals_t) vals_t[t] = __ldg(vals + j);
     if (perm_out) perm_out[t] = j;
   }
 }
@@ -386,13 +388,19 @@ int hpspmm_csr_transpose(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, con
   const size_t b_arr = align_up((size_t)nnz * 4, 256);
   const size_t b_hist = align_up((size_t)hist_n * 4, 256);
   const size_t b_tot = align_up((size_t)scan_blocks * 4, 256);
-  int st = hpspmm_ensure_scratch(ctx, 4 * b_arr + b_hist + b_tot);
+  int st = hpspmm_ensure_scratch(ctx, 5 * b_arr + b_hist + b_tot);
   if (st != HPSPMM_OK) return st;
   char* base = (char*)ctx->scratch;
   int* keys[2] = {(int*)base, (int*)(base + b_arr)};
   int* pays[2] = {(int*)(base + 2 * b_arr), (int*)(base + 3 * b_arr)};
-  int* hist = (int*)(base + 4 * b_arr);
-  int* totals = (int*)(base + 4 * b_arr + b_hist);
+  int* row_of = (int*)(base + 4 * b_arr);
+  int* hist = (int*)(base + 5 * b_arr);
+  int* totals = (int*)(base + 5 * b_arr + b_hist);
+
+  // source row of every entry (neighbouring threads search neighbouring entries: cache friendly)
+  expand_rows_kernel<<<grid_for(ctx, nnz), kThreads, 0, s>>>((int)M, nnz, nnz, row_ptr, nullptr, nullptr,
+                                                             row_of, nullptr, nullptr);
+  ctx->launches++;
 
   const int* kin = col_idx;
   const int* pin = nullptr;
@@ -412,8 +420,8 @@ int hpspmm_csr_transpose(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, con
     cur ^= 1;
   }
   transposed_row_ptr_kernel<<<grid_for(ctx, N + 1), kThreads, 0, s>>>(kin, nnz, N, row_ptr_t);
-  transposed_gather_kernel<<<grid_for(ctx, nnz), kThreads, 0, s>>>((int)M, nnz, row_ptr, vals, pin,
-                                                                   col_idx_t, vals_t, perm_out);
+  transposed_gather_kernel<<<grid_for(ctx, nnz), kThreads, 0, s>>>(nnz, row_of, vals, pin, col_idx_t,
+                                                                   vals_t, perm_out);
   ctx->launches += 2;
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;
