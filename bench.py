@@ -335,10 +335,10 @@ def main():
         e2e = {"value": 2.0 * nnz_total * sum(ks) / dt / 1e9, "unit": "GFLOPS",
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                "ms_per_step": dt * 1e3, "steps": args.e2e_steps}
-        # same chunking (plan and plan-less call pick the same chunk size for a given K), so the
-        # host entry point and the resident path must agree bit for bit
+        # the host entry point works in 32-column slabs, so rows split across chunks are summed in
+        # another order than on the resident path: equal within the parity tolerance, not bit for bit
         Kc = max(ks)
-        assert torch.equal(h_C[Kc], Cs[Kc].cpu()), "host entry point and device path disagree"
+        torch.testing.assert_close(h_C[Kc], Cs[Kc].cpu(), rtol=1e-4, atol=1e-3)
 
     # ---- roofline of the dominant kernel (largest K) -----------------------------------
     peak, peak_kind = load_peak()

@@ -59,6 +59,8 @@ int hpspmm_ctx_destroy(hpspmm_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->stage) cudaFree(ctx->stage);
   if (ctx->flag) cudaFree(ctx->flag);
+  for (int i = 0; i < 3; ++i)
+    if (ctx->pipe_streams[i]) cudaStreamDestroy(ctx->pipe_streams[i]);
   delete ctx;
   return HPSPMM_OK;
 }

@@ -23,6 +23,8 @@ struct hpspmm_ctx {
   void* stage;
   size_t stage_bytes;
   int* flag;  // one device int used by validation and plan building
+  // streams of the host-buffer entry point: uploads, kernels, downloads (created on first use)
+  cudaStream_t pipe_streams[3];
   char err[256];
 };
 

@@ -1042,6 +1042,101 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
                   chunk_row, carry_row, carry_val, chunk_order, true, s);
 }
 
+// Host-buffer product, pipelined over 32-column slabs when K is a multiple of 32 and K >= 64:
+// C[:, s] = A * B[:, s] needs only slab s of B, so slab s+1 is uploaded (strided 2-D copy)
+// while slab s is multiplied (as a contiguous K = 32 product) and slab s-1 is downloaded.
+// PCIe is full duplex: the downloads hide behind the uploads and the call costs about
+// upload(A) + upload(B) + download(one slab) instead of upload + download of everything.
+static int host_product_slabs(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz,
+                              const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
+                              const float* B, float* C, const hpspmm_opts* opts) {
+  // 64-column slabs when they divide K and leave at least two (256-byte rows copy faster than
+  // 128-byte rows when both directions are busy), else 32
+  const int64_t KS = (K % 64 == 0 && K >= 128) ? 64 : 32;
+  constexpr int NBUF = 2;
+  const int n_slabs = (int)(K / KS);
+  for (int i = 0; i < 3; ++i)
+    if (!ctx->pipe_streams[i])
+      HPSPMM_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->pipe_streams[i], cudaStreamNonBlocking));
+  cudaStream_t s_in = ctx->pipe_streams[0], s_run = ctx->pipe_streams[1], s_out = ctx->pipe_streams[2];
+  const size_t b_rp = align_up((size_t)(M + 1) * 4, 256);
+  const size_t b_nz = align_up((size_t)nnz * 4, 256);
+  const size_t b_Bs = align_up((size_t)N * KS * 4, 256);
+  const size_t b_Cs = align_up((size_t)M * KS * 4, 256);
+  int st = hpspmm_ensure_stage(ctx, b_rp + 2 * b_nz + NBUF * (b_Bs + b_Cs));
+  if (st != HPSPMM_OK) return st;
+  // size the kernel scratch before anything is queued (growing it synchronises the device)
+  {
+    const int32_t S = (opts && opts->chunk_nnz > 0) ? (opts->chunk_nnz + 31) / 32 * 32 : hpspmm_default_chunk_nnz(KS);
+    const int64_t n_chunks = (nnz + S - 1) / S;
+    const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
+    st = hpspmm_ensure_scratch(ctx, 4 * b_int + align_up((size_t)(n_chunks + 1) * KS * 4, 256) +
+                                        hpspmm_order_scratch_bytes(n_chunks));
+    if (st != HPSPMM_OK) return st;
+  }
+  char* base = (char*)ctx->stage;
+  int32_t* d_rp = (int32_t*)base;
+  int32_t* d_col = (int32_t*)(base + b_rp);
+  float* d_val = (float*)(base + b_rp + b_nz);
+  float* d_Bs[NBUF];
+  float* d_Cs[NBUF];
+  for (int i = 0; i < NBUF; ++i) {
+    d_Bs[i] = (float*)(base + b_rp + 2 * b_nz + i * b_Bs);
+    d_Cs[i] = (float*)(base + b_rp + 2 * b_nz + NBUF * b_Bs + i * b_Cs);
+  }
+  cudaEvent_t ev_a, ev_b[NBUF], ev_run[NBUF], ev_out[NBUF];
+  HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev_a, cudaEventDisableTiming));
+  for (int i = 0; i < NBUF; ++i) {
+    HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev_b[i], cudaEventDisableTiming));
+    HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev_run[i], cudaEventDisableTiming));
+    HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev_out[i], cudaEventDisableTiming));
+  }
+  int rc = HPSPMM_OK;
+  cudaError_t e = cudaSuccess;
+#define PIPE_TRY(call)                      \
+  if (rc == HPSPMM_OK && e == cudaSuccess) { \
+    e = (call);                             \
+  }
+  PIPE_TRY(cudaMemcpyAsync(d_rp, row_ptr, (size_t)(M + 1) * 4, cudaMemcpyHostToDevice, s_in));
+  PIPE_TRY(cudaMemcpyAsync(d_col, col_idx, (size_t)nnz * 4, cudaMemcpyHostToDevice, s_in));
+  PIPE_TRY(cudaMemcpyAsync(d_val, vals, (size_t)nnz * 4, cudaMemcpyHostToDevice, s_in));
+  PIPE_TRY(cudaEventRecord(ev_a, s_in));
+  PIPE_TRY(cudaStreamWaitEvent(s_run, ev_a, 0));
+  for (int s = 0; s < n_slabs; ++s) {
+    const int buf = s % NBUF;
+    // upload slab s once the product that last read this buffer is done
+    if (s >= NBUF) PIPE_TRY(cudaStreamWaitEvent(s_in, ev_run[buf], 0));
+    PIPE_TRY(cudaMemcpy2DAsync(d_Bs[buf], KS * 4, B + s * KS, (size_t)K * 4, KS * 4, (size_t)N,
+                               cudaMemcpyHostToDevice, s_in));
+    PIPE_TRY(cudaEventRecord(ev_b[buf], s_in));
+    // multiply once the slab has landed and the previous download from this C buffer is done
+    PIPE_TRY(cudaStreamWaitEvent(s_run, ev_b[buf], 0));
+    if (s >= NBUF) PIPE_TRY(cudaStreamWaitEvent(s_run, ev_out[buf], 0));
+    if (rc == HPSPMM_OK && e == cudaSuccess)
+      rc = hpspmm_spmm_csr_f32(ctx, nullptr, M, N, KS, nnz, d_rp, d_col, d_val, d_Bs[buf], d_Cs[buf], opts,
+                               (hpspmm_stream)s_run);
+    PIPE_TRY(cudaEventRecord(ev_run[buf], s_run));
+    // download
+    PIPE_TRY(cudaStreamWaitEvent(s_out, ev_run[buf], 0));
+    PIPE_TRY(cudaMemcpy2DAsync(C + s * KS, (size_t)K * 4, d_Cs[buf], KS * 4, KS * 4, (size_t)M,
+                               cudaMemcpyDeviceToHost, s_out));
+    PIPE_TRY(cudaEventRecord(ev_out[buf], s_out));
+  }
+#undef PIPE_TRY
+  // drain all three streams whatever happened, then release the events
+  cudaError_t e1 = cudaStreamSynchronize(s_in), e2 = cudaStreamSynchronize(s_run), e3 = cudaStreamSynchronize(s_out);
+  cudaEventDestroy(ev_a);
+  for (int i = 0; i < NBUF; ++i) {
+    cudaEventDestroy(ev_b[i]);
+    cudaEventDestroy(ev_run[i]);
+    cudaEventDestroy(ev_out[i]);
+  }
+  if (rc != HPSPMM_OK) return rc;
+  if (e == cudaSuccess) e = e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3);
+  if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "host-buffer product pipeline", e);
+  return HPSPMM_OK;
+}
+
 int hpspmm_spmm_csr_f32_host(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz,
                              const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
                              const float* B, float* C, const hpspmm_opts* opts) {
@@ -1052,6 +1147,9 @@ int hpspmm_spmm_csr_f32_host(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, i
   HPSPMM_REQUIRE(ctx, M == 0 || C != nullptr, "null output");
   if (M == 0) return HPSPMM_OK;
   hpspmm_device_guard guard(ctx->device);
+  const int algo = opts ? opts->algo : HPSPMM_ALGO_AUTO;
+  if (nnz > 0 && N > 0 && K >= 64 && K % 32 == 0 && algo != HPSPMM_ALGO_ROW_SPLIT)
+    return host_product_slabs(ctx, M, N, K, nnz, row_ptr, col_idx, vals, B, C, opts);
   const size_t b_rp = align_up((size_t)(M + 1) * 4, 256);
   const size_t b_nz = align_up((size_t)nnz * 4, 256);
   const size_t b_B = align_up((size_t)N * (size_t)K * 4, 256);

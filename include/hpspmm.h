@@ -176,7 +176,11 @@ HPSPMM_API int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M,
                                                   char* err_buf, size_t err_len);
 
 /* Same product with HOST buffers: copies A and B to the device, runs the product,
- * copies C back, synchronises.  This is the call the end-to-end figure is timed
+ * copies C back, synchronises.  When K is a multiple of 32 and at least 64 the call is
+ * pipelined over 32- or 64-column slabs of B and C (uploads, products and downloads overlap on
+ * three internal streams, PCIe being full duplex); each slab is a K = 32 product, so the
+ * rounding of rows split across chunks can differ from the device-pointer entry point in
+ * the last bits.  This is the call the end-to-end figure is timed
  * through; it is what the reference's driver does around GESpMM
  * (test/test_all.cpp:44-60 upload, :91-92 product) plus the download the
  * reference only performs inside its disabled checker (spmm/utils/compare.cpp:6-7). */

@@ -142,9 +142,10 @@ def test_full_size_cfg2_k32(gpu_ctx, pkg, oracle):
     assert np.all(C[deg == 0] == 0)
 
 
-def test_host_buffer_entry_point(gpu_ctx, pkg, oracle):
+@pytest.mark.parametrize("K", [32, 64, 128, 192, 96, 40])
+def test_host_buffer_entry_point(gpu_ctx, pkg, oracle, K):
+    """K = 64 / 96 / 128 / 192 take the slab pipeline (32- or 64-column slabs), the others the plain path."""
     g = pkg.gen_rmat(12, 16, seed=4)
-    K = 64
     B = pkg.host_fill_uniform(g["N"] * K, 4, 1, -1.0, 1.0).reshape(g["N"], K)
     C = np.full((g["M"], K), np.nan, dtype=np.float32)
     gpu_ctx.spmm_csr_host(g["M"], g["N"], K, g["nnz"], g["row_ptr"], g["col_idx"], g["vals"], B, C)
