@@ -93,7 +93,7 @@ def build_test_all(force=False, verbose=False):
             and os.path.getmtime(TEST_ALL_PATH) >= max(os.path.getmtime(src), os.path.getmtime(LIB_PATH))):
         return TEST_ALL_PATH
     cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++") or "g++")
-    _run([cxx, "-O2", "-std=c++17", "-fopenmp", "-I", os.path.join(ROOT, "include"), src, "-o",
+    _run([cxx, "-O3", "-mavx2", "-mfma", "-std=c++17", "-fopenmp", "-I", os.path.join(ROOT, "include"), src, "-o",
           TEST_ALL_PATH, "-L", LIB_DIR, "-lhpspmm", "-Wl,-rpath,$ORIGIN"], verbose)
     return TEST_ALL_PATH
 
