@@ -251,7 +251,7 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
   HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "negative size");
   HPSPMM_REQUIRE(ctx, K >= 1, "K must be >= 1");
-  if (M > 2147483646ll || N > 2147483647ll || nnz > 2147483647ll || K > (1 << 20)) {
+  if (M > 2147483646ll || N > 2147483647ll || nnz > 2147483647ll - 4096 || K > (1 << 20)) {
     snprintf(ctx->err, sizeof(ctx->err), "sizes beyond 32-bit CSR indices");
     return HPSPMM_ERR_UNSUPPORTED;
   }

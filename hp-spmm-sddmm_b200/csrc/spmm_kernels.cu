@@ -858,7 +858,8 @@ int check_spmm_args(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nn
   HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "negative size");
   HPSPMM_REQUIRE(ctx, K >= 1, "K must be >= 1");
-  if (M > 2147483646ll || N > 2147483647ll || nnz > 2147483647ll || K > (1 << 20)) {
+  // entry positions are 32-bit and the kernels look up to one tile past a chunk's end
+  if (M > 2147483646ll || N > 2147483647ll || nnz > 2147483647ll - 4096 || K > (1 << 20)) {
     snprintf(ctx->err, sizeof(ctx->err), "sizes beyond 32-bit CSR indices");
     return HPSPMM_ERR_UNSUPPORTED;
   }
@@ -919,7 +920,7 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* r
   *out = nullptr;
   HPSPMM_REQUIRE(ctx, M >= 0 && nnz >= 0 && max_K >= 1, "bad size");
   HPSPMM_REQUIRE(ctx, row_ptr != nullptr, "null row_ptr");
-  if (M > 2147483646ll || nnz > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
+  if (M > 2147483646ll || nnz > 2147483647ll - 4096) return HPSPMM_ERR_UNSUPPORTED;
   int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(max_K);
   S = (S + 31) / 32 * 32;
   hpspmm_device_guard guard(ctx->device);
