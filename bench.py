@@ -237,7 +237,8 @@ def main():
         Cs[K] = torch.empty((M_l, K), dtype=torch.float32, device=dev)
     # one plan per product width: the nominal chunk size is chosen from K, and a GNN layer
     # reuses its plan across epochs
-    plans = {K: ctx.plan_create(M_l, nnz_l, t_rp.data_ptr(), K, None, sptr) for K in ks}
+    plans = {K: ctx.plan_create(M_l, nnz_l, t_rp.data_ptr(), K, None, sptr, N=N,
+                                col_idx=t_ci.data_ptr()) for K in ks}
     plan_info = {str(K): ctx.plan_info(plans[K]) for K in ks}
 
     # --b-sharded: each rank owns N / world rows of B; the gathered copy is what the kernel reads

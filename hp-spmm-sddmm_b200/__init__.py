@@ -86,7 +86,7 @@ PROTOTYPES = {
     "hpspmm_host_fill_uniform_f32": (c_int, [_P, _I64, c_uint64, c_uint64, c_float, c_float]),
     "hpspmm_spmm_csr_f32": (c_int, [_P, _P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P,
                                     POINTER(Opts), _P]),
-    "hpspmm_plan_create": (c_int, [_P, _I64, _I64, _P, _I64, POINTER(Opts), _P, POINTER(_P)]),
+    "hpspmm_plan_create": (c_int, [_P, _I64, _I64, _I64, _P, _P, _I64, POINTER(Opts), _P, POINTER(_P)]),
     "hpspmm_plan_destroy": (c_int, [_P, _P]),
     "hpspmm_plan_info": (c_int, [_P, POINTER(_I64), POINTER(_I64), POINTER(_I64), POINTER(_I64)]),
     "hpspmm_spmm_csr_f32_static_scratch": (c_int, [c_int, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P,
@@ -253,9 +253,12 @@ class Context:
         return ms.value
 
     # -- the path -------------------------------------------------------------------
-    def plan_create(self, M, nnz, row_ptr, max_K, opts=None, stream=None):
+    def plan_create(self, M, nnz, row_ptr, max_K, opts=None, stream=None, N=0, col_idx=None):
+        """Chunk table for (M, nnz, row_ptr).  With N and col_idx the pieces of heavy rows are also
+        ordered by the column band they read (better L2 reuse of B)."""
         p = _P()
-        self._check(self.lib.hpspmm_plan_create(self.handle, M, nnz, _ptr(row_ptr), max_K,
+        self._check(self.lib.hpspmm_plan_create(self.handle, M, N, nnz, _ptr(row_ptr),
+                                                _ptr(col_idx) if col_idx is not None else None, max_K,
                                                 byref(opts) if opts else None, stream, byref(p)),
                     "hpspmm_plan_create")
         return p

@@ -98,12 +98,14 @@ int hpspmm_launch_chunk_table(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int
                               int32_t* chunk_row, int* split_count, cudaStream_t stream);
 
 // Processing order of the chunks: chunk ids sorted by estimated cost (entries / 8 + rows / 2),
-// most expensive first (a stable 8-bit counting sort on the device).  Chunks full of short
-// rows take several times longer than chunks inside one heavy row; started last they leave the
-// GPU draining, started first they overlap with the cheap ones.  `scratch` needs
-// hpspmm_order_scratch_bytes(n_chunks) bytes.
+// most expensive first (stable 8-bit counting-sort passes on the device).  Chunks full of short
+// rows started last leave the GPU draining; started first they overlap with the others.
+// With col_idx (may be null) the chunks that lie inside one row come last, in ascending order
+// of their first column, so that pieces of different heavy rows running together read the same
+// band of B.  `scratch` needs hpspmm_order_scratch_bytes(n_chunks) bytes.
 size_t hpspmm_order_scratch_bytes(int64_t n_chunks);
-int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t n_chunks, const int32_t* chunk_start,
+int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t n_chunks,
+                                const int32_t* row_ptr, const int32_t* col_idx, const int32_t* chunk_start,
                                 const int32_t* chunk_row, int32_t* order_out, void* scratch,
                                 cudaStream_t stream);
 

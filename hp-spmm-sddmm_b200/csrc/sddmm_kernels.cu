@@ -288,7 +288,8 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
     int32_t* co = (int32_t*)((char*)ctx->scratch + 2 * b_int);
     st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, cs, cr, nullptr, s);
     if (st != HPSPMM_OK) return st;
-    st = hpspmm_order_chunks_by_cost(ctx, M, n_chunks, cs, cr, co, (char*)ctx->scratch + 3 * b_int, s);
+    st = hpspmm_order_chunks_by_cost(ctx, M, N, n_chunks, row_ptr, nullptr, cs, cr, co,
+                                     (char*)ctx->scratch + 3 * b_int, s);
     if (st != HPSPMM_OK) return st;
     chunk_start = cs;
     chunk_row = cr;

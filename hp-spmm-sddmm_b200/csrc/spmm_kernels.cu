@@ -913,12 +913,12 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
 
 extern "C" {
 
-int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
-                       int64_t max_K, const hpspmm_opts* opts, hpspmm_stream stream,
-                       hpspmm_plan** out) {
+int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
+                       const int32_t* col_idx, int64_t max_K, const hpspmm_opts* opts,
+                       hpspmm_stream stream, hpspmm_plan** out) {
   HPSPMM_REQUIRE(ctx, ctx != nullptr && out != nullptr, "null context or output");
   *out = nullptr;
-  HPSPMM_REQUIRE(ctx, M >= 0 && nnz >= 0 && max_K >= 1, "bad size");
+  HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0 && max_K >= 1, "bad size");
   HPSPMM_REQUIRE(ctx, row_ptr != nullptr, "null row_ptr");
   if (M > 2147483646ll || nnz > 2147483647ll - 4096) return HPSPMM_ERR_UNSUPPORTED;
   int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(max_K);
@@ -960,8 +960,8 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* r
     st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, p->n_chunks, p->chunk_start,
                                    p->chunk_row, ctx->flag, s);
   if (e == cudaSuccess && st == HPSPMM_OK && M > 0)
-    st = hpspmm_order_chunks_by_cost(ctx, M, p->n_chunks, p->chunk_start, p->chunk_row, p->chunk_order,
-                                     sort_scratch, s);
+    st = hpspmm_order_chunks_by_cost(ctx, M, N, p->n_chunks, row_ptr, col_idx, p->chunk_start, p->chunk_row,
+                                     p->chunk_order, sort_scratch, s);
   if (e == cudaSuccess && st == HPSPMM_OK)
     e = cudaMemcpyAsync(&split, ctx->flag, sizeof(int), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess && st == HPSPMM_OK) e = cudaStreamSynchronize(s);
@@ -1037,7 +1037,9 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
   st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, chunk_start, chunk_row,
                                  nullptr, s);
   if (st != HPSPMM_OK) return st;
-  st = hpspmm_order_chunks_by_cost(ctx, M, n_chunks, chunk_start, chunk_row, chunk_order, sort_scratch, s);
+  // cost order only: the second sort pass of the column-band order costs more per call than it saves
+  st = hpspmm_order_chunks_by_cost(ctx, M, N, n_chunks, row_ptr, nullptr, chunk_start, chunk_row, chunk_order,
+                                   sort_scratch, s);
   if (st != HPSPMM_OK) return st;
   return run_spmm(ctx, hint, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
                   chunk_row, carry_row, carry_val, chunk_order, true, s);

@@ -251,20 +251,35 @@ __global__ void transposed_gather_kernel(int64_t nnz, const int* __restrict__ ro
   }
 }
 
-// Cost estimate of chunk c in arbitrary units: entries / 8 (gather batches) + rows / 2 (each
-// row end costs a cross-group reduction, a store and a step along row_ptr), capped at 255.
-// key = 255 - cost, so ascending keys put the most expensive chunks first.
+// Sort key of chunk c (ascending = earlier).  Without col_idx: 255 - cost (8 bits).  With col_idx, 16 bits:
+//   Chunks that span row ends: (255 - cost) << 7 with cost = entries / 8 (gather batches) + rows / 2
+//   (each row end costs a cross-group reduction, a store and a step along row_ptr), capped at 255:
+//   the most expensive first.
+//   Chunks that lie inside one row (pieces of heavy rows): 32768 + (first column >> col_shift), so that
+//   they follow all the others and run in ascending order of the column band they gather from.  Column
+//   indices ascend inside a row, so pieces of different heavy rows that run at the same time read the
+//   same band of B and find it in L2.  Without col_idx these chunks sort by cost like the rest.
 __global__ void chunk_cost_key_kernel(int M, int64_t n_chunks, const int* __restrict__ chunk_start,
-                                      const int* __restrict__ chunk_row, int* __restrict__ keys) {
+                                      const int* __restrict__ chunk_row, const int* __restrict__ row_ptr,
+                                      const int* __restrict__ col_idx, int col_shift,
+                                      int* __restrict__ keys) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += stride) {
     const int next = c + 1 < n_chunks ? chunk_row[c + 1] : M;
-    int rows = next - chunk_row[c];
+    const int r0 = chunk_row[c];
+    int rows = next - r0;
     rows = rows < 0 ? 0 : rows;
-    const int entries = chunk_start[c + 1] - chunk_start[c];
+    const int n0 = chunk_start[c], n1 = chunk_start[c + 1];
+    const int entries = n1 - n0;
     int cost = (entries >> 3) + (rows >> 1);
     cost = cost > 255 ? 255 : cost;
-    keys[c] = 255 - cost;
+    int key = 255 - cost;
+    if (col_idx != nullptr) {
+      key <<= 7;
+      if (entries >= 32 && r0 < M && __ldg(row_ptr + r0 + 1) >= n1)
+        key = 32768 + min(32767, __ldg(col_idx + n0) >> col_shift);
+    }
+    keys[c] = key;
   }
 }
 
@@ -283,11 +298,12 @@ size_t hpspmm_order_scratch_bytes(int64_t n_chunks) {
   const int64_t n_tiles = (n + kTile - 1) / kTile;
   const int64_t hist_n = 256 * n_tiles;
   const int64_t scan_blocks = (hist_n + kScanTile - 1) / kScanTile;
-  return 2 * align_up((size_t)n * 4, 256) + align_up((size_t)hist_n * 4, 256) +
+  return 3 * align_up((size_t)n * 4, 256) + align_up((size_t)hist_n * 4, 256) +
          align_up((size_t)scan_blocks * 4, 256);
 }
 
-int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t n_chunks, const int32_t* chunk_start,
+int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t n_chunks,
+                                const int32_t* row_ptr, const int32_t* col_idx, const int32_t* chunk_start,
                                 const int32_t* chunk_row, int32_t* order_out, void* scratch,
                                 cudaStream_t stream) {
   if (n_chunks <= 0) return HPSPMM_OK;
@@ -297,18 +313,30 @@ int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t n_chunks, co
   const size_t b_arr = align_up((size_t)n_chunks * 4, 256);
   char* base = (char*)scratch;
   int* keys = (int*)base;
-  int* keys_sorted = (int*)(base + b_arr);
-  int* hist = (int*)(base + 2 * b_arr);
-  int* totals = (int*)(base + 2 * b_arr + align_up((size_t)hist_n * 4, 256));
-  chunk_cost_key_kernel<<<grid_for(ctx, n_chunks), kThreads, 0, stream>>>((int)M, n_chunks, chunk_start,
-                                                                          chunk_row, keys);
-  radix_hist_kernel<<<n_tiles, kThreads, 0, stream>>>(keys, n_chunks, 0, n_tiles, hist);
-  scan_block_totals_kernel<<<(unsigned)scan_blocks, kThreads, 0, stream>>>(hist, hist_n, totals);
-  scan_single_block_kernel<<<1, kThreads, 0, stream>>>(totals, scan_blocks);
-  scan_rescan_kernel<<<(unsigned)scan_blocks, kThreads, 0, stream>>>(hist, hist_n, totals);
-  radix_scatter_kernel<<<n_tiles, kThreads, 0, stream>>>(keys, nullptr, n_chunks, 0, n_tiles, hist,
-                                                        keys_sorted, order_out);
-  ctx->launches += 6;
+  int* keys_tmp = (int*)(base + b_arr);
+  int* order_tmp = (int*)(base + 2 * b_arr);
+  int* hist = (int*)(base + 3 * b_arr);
+  int* totals = (int*)(base + 3 * b_arr + align_up((size_t)hist_n * 4, 256));
+  int col_shift = 0;
+  while (((N > 0 ? N - 1 : 0) >> col_shift) > 32767) ++col_shift;
+  chunk_cost_key_kernel<<<grid_for(ctx, n_chunks), kThreads, 0, stream>>>(
+      (int)M, n_chunks, chunk_start, chunk_row, row_ptr, col_idx, col_shift, keys);
+  ctx->launches++;
+  // stable 8-bit passes, low digit first: one for the 8-bit key, two for the 16-bit key
+  const int passes = col_idx ? 2 : 1;
+  for (int pass = 0; pass < passes; ++pass) {
+    const int* kin = pass == 0 ? keys : keys_tmp;
+    const int* pin = pass == 0 ? nullptr : order_tmp;
+    int* kout = pass == 0 ? keys_tmp : keys;
+    int* pout = pass == passes - 1 ? order_out : order_tmp;
+    radix_hist_kernel<<<n_tiles, kThreads, 0, stream>>>(kin, n_chunks, 8 * pass, n_tiles, hist);
+    scan_block_totals_kernel<<<(unsigned)scan_blocks, kThreads, 0, stream>>>(hist, hist_n, totals);
+    scan_single_block_kernel<<<1, kThreads, 0, stream>>>(totals, scan_blocks);
+    scan_rescan_kernel<<<(unsigned)scan_blocks, kThreads, 0, stream>>>(hist, hist_n, totals);
+    radix_scatter_kernel<<<n_tiles, kThreads, 0, stream>>>(kin, pin, n_chunks, 8 * pass, n_tiles, hist, kout,
+                                                          pout);
+    ctx->launches += 5;
+  }
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;
 }

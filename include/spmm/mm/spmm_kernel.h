@@ -26,7 +26,8 @@ inline void HPSpMM(const CSR_Matrix& mat1, const Matrix& mat2, Matrix& result, f
   hpspmm_opts opts = {algo, 0, 0, 0};
   hpspmm_plan* plan = nullptr;
   if (algo != HPSPMM_ALGO_ROW_SPLIT)
-    hpspmm::check(hpspmm_plan_create(ctx, M, nnz, mat1.row_offsets().data<int32_t>(), K, &opts, nullptr, &plan),
+    hpspmm::check(hpspmm_plan_create(ctx, M, N, nnz, mat1.row_offsets().data<int32_t>(),
+                                     mat1.column_indices().data<int32_t>(), K, &opts, nullptr, &plan),
                   "hpspmm_plan_create");
   auto once = [&]() {
     hpspmm::check(hpspmm_spmm_csr_f32(ctx, plan, M, N, K, nnz, mat1.row_offsets().data<int32_t>(),
@@ -98,7 +99,8 @@ inline void HPSDDMM(const CSR_Matrix& pattern, const Matrix& X, const Matrix& Y,
   if (X.dim(0) != M || Y.dim(0) != N || Y.dim(1) != K || out_vals.size() != nnz)
     throw hpspmm::Error(HPSPMM_ERR_INVALID, "SDDMM operand shapes do not agree");
   hpspmm_plan* plan = nullptr;
-  hpspmm::check(hpspmm_plan_create(ctx, M, nnz, pattern.row_offsets().data<int32_t>(), K, nullptr, nullptr, &plan),
+  hpspmm::check(hpspmm_plan_create(ctx, M, N, nnz, pattern.row_offsets().data<int32_t>(),
+                                   pattern.column_indices().data<int32_t>(), K, nullptr, nullptr, &plan),
                 "hpspmm_plan_create");
   auto once = [&]() {
     hpspmm::check(hpspmm_sddmm_csr_f32(ctx, plan, M, N, K, nnz, pattern.row_offsets().data<int32_t>(),

@@ -80,7 +80,8 @@ def guarded_output(ctx, shape, fill=np.float32(-777.25)):
     return buf, payload, read
 
 
-def gpu_spmm(ctx, pkg, row_ptr, col_idx, vals, B, N=None, opts=None, use_plan=False, guard=True):
+def gpu_spmm(ctx, pkg, row_ptr, col_idx, vals, B, N=None, opts=None, use_plan=False, guard=True,
+             plan_cols=True):
     M = len(row_ptr) - 1
     N = B.shape[0] if N is None else N
     K = B.shape[1]
@@ -89,7 +90,7 @@ def gpu_spmm(ctx, pkg, row_ptr, col_idx, vals, B, N=None, opts=None, use_plan=Fa
     buf, c_ptr, read = guarded_output(ctx, (M, K))
     plan = None
     if use_plan:
-        plan = ctx.plan_create(M, nnz, d_rp, K, opts)
+        plan = ctx.plan_create(M, nnz, d_rp, K, opts, N=N, col_idx=d_ci if plan_cols else None)
     ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_B, c_ptr, plan=plan, opts=opts)
     ctx.stream_sync()
     C = read()

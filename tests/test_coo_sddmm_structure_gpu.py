@@ -65,7 +65,7 @@ def test_sddmm(gpu_ctx, pkg, oracle, K, use_plan):
     Y = pkg.host_fill_uniform(N * K, 7, 2, -1.0, 1.0).reshape(N, K)
     d_rp, d_ci, d_X, d_Y = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"]), ctx.upload(X), ctx.upload(Y)
     buf, o_ptr, read = guarded_output(ctx, (nnz,))
-    plan = ctx.plan_create(M, nnz, d_rp, K) if use_plan else None
+    plan = ctx.plan_create(M, nnz, d_rp, K, N=N, col_idx=d_ci) if use_plan else None
     ctx.sddmm_csr(M, N, K, nnz, d_rp, d_ci, d_X, d_Y, o_ptr, plan=plan)
     ctx.stream_sync()
     out = read()

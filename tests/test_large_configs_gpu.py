@@ -19,7 +19,7 @@ def _rows_vs_rowsums(ctx, pkg, g, K, sample_rows, use_plan=True):
     ctx.fill(d_B, N * K, 1.0)
     d_C = ctx.alloc((M, K), np.float32)
     ctx.fill(d_C, M * K, -5.0)                      # stale data must be overwritten everywhere
-    plan = ctx.plan_create(M, nnz, d_rp, K) if use_plan else None
+    plan = ctx.plan_create(M, nnz, d_rp, K, N=N, col_idx=d_ci) if use_plan else None
     ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_B, d_C, plan=plan)
     ctx.stream_sync()
     rp = g["row_ptr"].astype(np.int64)
@@ -98,7 +98,7 @@ def test_cfg5_gnn_layer_full_size(gpu_ctx, pkg, oracle):
     d_H, d_dC = ctx.upload(H), ctx.upload(dC)
     d_C = ctx.alloc((M, K), np.float32)
     d_dA = ctx.alloc((nnz,), np.float32)
-    plan = ctx.plan_create(M, nnz, d_rp, K)
+    plan = ctx.plan_create(M, nnz, d_rp, K, N=N, col_idx=d_ci)
     # forward
     ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_H, d_C, plan=plan)
     ref, abs_sum = oracle.spmm_f64(g["row_ptr"], g["col_idx"], g["vals"], H)
@@ -114,7 +114,7 @@ def test_cfg5_gnn_layer_full_size(gpu_ctx, pkg, oracle):
     assert np.array_equal(d_rpt.to_host(), rpt) and np.array_equal(d_cit.to_host(), cit)
     assert np.array_equal(d_vt.to_host(), vt)
     d_dH = ctx.alloc((N, K), np.float32)
-    plan_t = ctx.plan_create(N, nnz, d_rpt, K)
+    plan_t = ctx.plan_create(N, nnz, d_rpt, K, N=M, col_idx=d_cit)
     ctx.spmm_csr(N, M, K, nnz, d_rpt, d_cit, d_vt, d_dC, d_dH, plan=plan_t)
     ref, abs_sum = oracle.spmm_f64(rpt, cit, vt, dC)
     check_against_f64(d_dH.to_host(), ref, abs_sum, "cfg5 backward")

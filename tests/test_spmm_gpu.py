@@ -113,7 +113,10 @@ def test_run_to_run_determinism(gpu_ctx, pkg):
     first = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B)
     for _ in range(3):
         assert np.array_equal(first, gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B))
+    # the order in which chunks are scheduled (by cost; with col_idx also by column band) never changes a bit
     assert np.array_equal(first, gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B, use_plan=True))
+    assert np.array_equal(first, gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B, use_plan=True,
+                                          plan_cols=False))
 
 
 def test_overwrites_stale_output_and_linearity(gpu_ctx, pkg, oracle):
