@@ -97,6 +97,15 @@ PROTOTYPES = {
     "hpspmm_sddmm_csr_f32": (c_int, [_P, _P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P,
                                      POINTER(Opts), _P]),
     "hpspmm_csr_transpose": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "hpspmm_layer_create": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _I64, _P, POINTER(_P)]),
+    "hpspmm_layer_destroy": (c_int, [_P, _P]),
+    "hpspmm_layer_info": (c_int, [_P, POINTER(_I64), POINTER(_I64), POINTER(_I64), POINTER(_I64),
+                                  POINTER(_I64)]),
+    "hpspmm_layer_transposed": (c_int, [_P, POINTER(_P), POINTER(_P), POINTER(_P), POINTER(_P)]),
+    "hpspmm_layer_forward": (c_int, [_P, _P, _I64, _P, _P, _P]),
+    "hpspmm_layer_backward_features": (c_int, [_P, _P, _I64, _P, _P, _P]),
+    "hpspmm_layer_backward_weights": (c_int, [_P, _P, _I64, _P, _P, _P, _P]),
+    "hpspmm_layer_update_values": (c_int, [_P, _P, _P, _P]),
     "hpspmm_padded_nnz": (_I64, [_I64, _I64]),
     "hpspmm_csr_to_coo_padded": (c_int, [_P, _I64, _I64, _P, _P, _P, _I64, _P, _P, _P, _P]),
     "hpspmm_validate_csr": (c_int, [_P, _I64, _I64, _I64, _P, _P, POINTER(_I64), _P]),
@@ -323,6 +332,55 @@ class Context:
 
 
 # ---- host side ---------------------------------------------------------------------------
+
+class Layer:
+    """One aggregation layer C = A·H with both backward products (hpspmm_layer_* of the C ABI).
+
+    row_ptr, col_idx and vals are device arrays (DeviceBuffer or raw addresses) that the caller
+    keeps alive.  All products run on `stream` and only enqueue work."""
+
+    def __init__(self, ctx, M, N, nnz, row_ptr, col_idx, vals, max_K, stream=None):
+        self.ctx, self.M, self.N, self.nnz, self.max_K = ctx, M, N, nnz, max_K
+        h = _P()
+        ctx._check(ctx.lib.hpspmm_layer_create(ctx.handle, M, N, nnz, _ptr(row_ptr), _ptr(col_idx), _ptr(vals),
+                                               max_K, stream, byref(h)), "hpspmm_layer_create")
+        self.handle = h
+
+    def close(self):
+        if self.handle:
+            self.ctx.lib.hpspmm_layer_destroy(self.ctx.handle, self.handle)
+            self.handle = None
+
+    def info(self):
+        v = [_I64() for _ in range(5)]
+        self.ctx._check(self.ctx.lib.hpspmm_layer_info(self.handle, *[byref(x) for x in v]), "hpspmm_layer_info")
+        return dict(zip(("M", "N", "nnz", "max_K", "owned_bytes"), (x.value for x in v)))
+
+    def transposed(self):
+        """Device addresses of the transpose the layer owns: row_ptr_t, col_idx_t, vals_t, perm."""
+        v = [_P() for _ in range(4)]
+        self.ctx._check(self.ctx.lib.hpspmm_layer_transposed(self.handle, *[byref(x) for x in v]),
+                        "hpspmm_layer_transposed")
+        return tuple(x.value for x in v)
+
+    def forward(self, K, H, C, stream=None):
+        self.ctx._check(self.ctx.lib.hpspmm_layer_forward(self.ctx.handle, self.handle, K, _ptr(H), _ptr(C),
+                                                          stream), "hpspmm_layer_forward")
+
+    def backward_features(self, K, dC, dH, stream=None):
+        self.ctx._check(self.ctx.lib.hpspmm_layer_backward_features(self.ctx.handle, self.handle, K, _ptr(dC),
+                                                                    _ptr(dH), stream),
+                        "hpspmm_layer_backward_features")
+
+    def backward_weights(self, K, dC, H, dA, stream=None):
+        self.ctx._check(self.ctx.lib.hpspmm_layer_backward_weights(self.ctx.handle, self.handle, K, _ptr(dC),
+                                                                   _ptr(H), _ptr(dA), stream),
+                        "hpspmm_layer_backward_weights")
+
+    def update_values(self, vals, stream=None):
+        self.ctx._check(self.ctx.lib.hpspmm_layer_update_values(self.ctx.handle, self.handle, _ptr(vals), stream),
+                        "hpspmm_layer_update_values")
+
 
 def _export_graph(lib, g):
     M, N, nnz = _I64(), _I64(), _I64()

@@ -24,6 +24,7 @@ SOURCES = [
     "spmm_kernels.cu",
     "sddmm_kernels.cu",
     "structure_kernels.cu",
+    "graph_layer.cu",
     "host_side.cpp",
 ]
 

@@ -224,6 +224,42 @@ HPSPMM_API int hpspmm_csr_transpose(hpspmm_ctx* ctx, int64_t M, int64_t N, int64
                                     const float* vals, int32_t* row_ptr_t, int32_t* col_idx_t,
                                     float* vals_t, int32_t* perm_out, hpspmm_stream stream);
 
+/* ---- aggregation layer: forward product, both backward products, cached structure -------
+ * One handle per sparse operand A of a GNN aggregation C = A * H.  It owns what a training
+ * loop would otherwise rebuild every step: the chunk tables of A and of its transpose, the
+ * transpose itself (built on the device), and the permutation that carries new edge
+ * weights into the transpose.  row_ptr, col_idx and vals are borrowed device arrays that
+ * must outlive the handle.  The reference has no counterpart: its driver issues single
+ * products (test/test_all.cpp:63-107) and ships neither a transpose nor an SDDMM.
+ *   forward            C  = A  * H        H is N x K, C is M x K
+ *   backward_features  dH = A^T * dC      dC is M x K, dH is N x K
+ *   backward_weights   dA[j] = dot(dC[row(j),:], H[col[j],:])   (nnz values, CSR order)
+ *   update_values      new vals pointer; the transpose's values are re-gathered from it
+ * create synchronises the stream (it builds two plans); the other calls only enqueue.
+ * Calls on one handle must not overlap on the GPU. */
+typedef struct hpspmm_layer hpspmm_layer;
+HPSPMM_API int hpspmm_layer_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz,
+                                   const int32_t* row_ptr, const int32_t* col_idx,
+                                   const float* vals, int64_t max_K, hpspmm_stream stream,
+                                   hpspmm_layer** out);
+HPSPMM_API int hpspmm_layer_destroy(hpspmm_ctx* ctx, hpspmm_layer* layer);
+HPSPMM_API int hpspmm_layer_info(const hpspmm_layer* layer, int64_t* M, int64_t* N, int64_t* nnz,
+                                 int64_t* max_K, int64_t* owned_bytes);
+/* device pointers to the transpose the handle owns (row_ptr_t[N+1], col_idx_t, vals_t, perm) */
+HPSPMM_API int hpspmm_layer_transposed(const hpspmm_layer* layer, const int32_t** row_ptr_t,
+                                       const int32_t** col_idx_t, const float** vals_t,
+                                       const int32_t** perm);
+HPSPMM_API int hpspmm_layer_forward(hpspmm_ctx* ctx, const hpspmm_layer* layer, int64_t K,
+                                    const float* H, float* C, hpspmm_stream stream);
+HPSPMM_API int hpspmm_layer_backward_features(hpspmm_ctx* ctx, const hpspmm_layer* layer,
+                                              int64_t K, const float* dC, float* dH,
+                                              hpspmm_stream stream);
+HPSPMM_API int hpspmm_layer_backward_weights(hpspmm_ctx* ctx, const hpspmm_layer* layer,
+                                             int64_t K, const float* dC, const float* H,
+                                             float* dA, hpspmm_stream stream);
+HPSPMM_API int hpspmm_layer_update_values(hpspmm_ctx* ctx, hpspmm_layer* layer,
+                                          const float* vals, hpspmm_stream stream);
+
 /* ---- CSR -> padded COO (device) ------------------------------------------------------
  * Replaces the host loops of get_coo_mat_from_smtx (spmm/mm/spmm_common.cpp:210-226):
  * row_out[j] = row of entry j, then (0, 0, 0.0f) padding up to a multiple of `padding`.

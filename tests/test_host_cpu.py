@@ -130,3 +130,29 @@ def test_context_needs_a_gpu_or_fails_loudly(pkg):
         pytest.skip("GPU present")
     with pytest.raises(pkg.HpspmmError):
         pkg.Context(0)
+
+
+def test_torch_front_end_registers_and_has_no_cpu_path(pkg):
+    """The autograd front-end imports without a GPU, registers its three operators, and refuses CPU tensors."""
+    import importlib
+    import torch
+    ops = importlib.import_module(pkg.__name__ + ".torch_ops")
+    for name in ("layer_forward", "layer_backward_features", "layer_backward_weights"):
+        assert hasattr(torch.ops.hpspmm, name)
+    rp = torch.zeros(5, dtype=torch.int32)
+    ci = torch.zeros(0, dtype=torch.int32)
+    v = torch.zeros(0, dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.TorchLayer(rp, ci, v, 4, 4, 32)
+    with pytest.raises(RuntimeError, match="unknown or closed"):
+        ops.layer_forward(torch.zeros(4, 32), v, 12345)
+    # the shape functions need no device
+    ops._layers[-1] = {"M": 7, "N": 4, "nnz": 9}
+    try:
+        with torch._subclasses.fake_tensor.FakeTensorMode():
+            H = torch.empty(4, 32)
+            assert ops.layer_forward(H, torch.empty(9), -1).shape == (7, 32)
+            assert ops.layer_backward_features(torch.empty(7, 32), torch.empty(9), -1).shape == (4, 32)
+            assert ops.layer_backward_weights(torch.empty(7, 32), H, -1).shape == (9,)
+    finally:
+        del ops._layers[-1]
