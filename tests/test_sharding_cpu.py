@@ -68,6 +68,78 @@ def test_two_rank_row_sharding_gloo(tmp_path, pkg, oracle, b_sharded):
     assert sum(nnz) == g["nnz"] and abs(nnz[0] - nnz[1]) <= 2 * np.diff(g["row_ptr"]).max()
 
 
+class _OracleLocal:
+    """Stand-in for the GPU products so that the exchange logic of ShardedLayer runs on CPU ranks."""
+
+    def __init__(self, oracle_lib, rp, ci, v, M_own, N):
+        self.o, self.rp, self.ci, self.v, self.M_own, self.N = oracle_lib, rp, ci, v, M_own, N
+        self.rpt, self.cit, self.vt, _ = oracle_lib.csr_transpose(M_own, N, rp, ci, v)
+
+    def forward(self, H):
+        import torch
+        return torch.from_numpy(self.o.spmm_f32(self.rp, self.ci, self.v, H.numpy()))
+
+    def backward_features(self, dC, out):
+        import torch
+        out.copy_(torch.from_numpy(self.o.spmm_f32(self.rpt, self.cit, self.vt, dC.numpy())))
+        return out
+
+    def backward_weights(self, dC, H):
+        import torch
+        ref, _ = self.o.sddmm_f64(self.rp, self.ci, dC.numpy(), H.numpy())
+        return torch.from_numpy(ref.astype(np.float32))
+
+
+def _layer_rank_main(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import importlib
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    import oracle_lib
+    pkg = entry.load_package()
+    sharded = importlib.import_module(pkg.__name__ + ".sharded")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = pkg.gen_rmat(10, 16, seed=23)
+    N, K = g["N"], 32
+    bounds = pkg.shard_bounds(g["row_ptr"], world)
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    rp, ci, v = pkg.shard_csr(g["row_ptr"], g["col_idx"], g["vals"], lo, hi)
+    H = pkg.host_fill_uniform(N * K, 23, 1, -1.0, 1.0).reshape(N, K)
+    dC = pkg.host_fill_uniform(N * K, 23, 2, -1.0, 1.0).reshape(N, K)
+    layer = sharded.ShardedLayer(_OracleLocal(oracle_lib, rp, ci, v, hi - lo, N), N, bounds, rank, world)
+    C_own = layer.forward(torch.from_numpy(np.ascontiguousarray(H[lo:hi])))
+    dC_own = torch.from_numpy(np.ascontiguousarray(dC[lo:hi]))
+    dH_own = layer.backward_features(dC_own)
+    dA_own = layer.backward_weights(dC_own)
+    for name, t in (("c", C_own), ("dh", dH_own), ("da", dA_own)):
+        np.save(os.path.join(out_dir, "%s_%d.npy" % (name, rank)), t.numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_layer_exchange_gloo(tmp_path, pkg, oracle, world):
+    """Forward all-gather, backward reduce-scatter and the SDDMM on the gathered features, on CPU ranks."""
+    import torch.multiprocessing as mp
+    from helpers import check_against_f64
+    mp.spawn(_layer_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    g = pkg.gen_rmat(10, 16, seed=23)
+    N, K = g["N"], 32
+    H = pkg.host_fill_uniform(N * K, 23, 1, -1.0, 1.0).reshape(N, K)
+    dC = pkg.host_fill_uniform(N * K, 23, 2, -1.0, 1.0).reshape(N, K)
+    cat = lambda name: np.concatenate([np.load(tmp_path / ("%s_%d.npy" % (name, r))) for r in range(world)])
+    assert np.array_equal(cat("c"), oracle.spmm_f32(g["row_ptr"], g["col_idx"], g["vals"], H))
+    rpt, cit, vt, _ = oracle.csr_transpose(g["M"], N, g["row_ptr"], g["col_idx"], g["vals"])
+    ref, abs_sum = oracle.spmm_f64(rpt, cit, vt, dC)
+    check_against_f64(cat("dh"), ref, abs_sum, "sharded dH")       # summed across ranks: order differs
+    ref, abs_sum = oracle.sddmm_f64(g["row_ptr"], g["col_idx"], dC, H)
+    check_against_f64(cat("da"), ref, abs_sum, "sharded dA")
+
+
 def test_shards_tile_the_matrix_for_every_world_size(pkg, oracle):
     g = pkg.gen_erdos_renyi(5000, 5000, 20.0, seed=22)
     B = pkg.host_fill_uniform(5000 * 32, 22, 1, -1.0, 1.0).reshape(5000, 32)
