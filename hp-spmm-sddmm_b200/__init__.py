@@ -108,6 +108,12 @@ PROTOTYPES = {
     "hpspmm_layer_update_values": (c_int, [_P, _P, _P, _P]),
     "hpspmm_padded_nnz": (_I64, [_I64, _I64]),
     "hpspmm_csr_to_coo_padded": (c_int, [_P, _I64, _I64, _P, _P, _P, _I64, _P, _P, _P, _P]),
+    "hpspmm_csr_to_coo_reordered": (c_int, [_P, _I64, _I64, _P, _P, _P, _P, _I64, _P, _P, _P, _P]),
+    "hpspmm_csr_permute": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "hpspmm_order_rows_by_degree": (c_int, [_P, _I64, _P, _P, _P]),
+    "hpspmm_invert_permutation": (c_int, [_P, _I64, _P, _P, _P]),
+    "hpspmm_gather_rows_f32": (c_int, [_P, _I64, _I64, _P, _P, _P, _P]),
+    "hpspmm_read_row_order": (c_int, [c_char_p, _I64, _P]),
     "hpspmm_validate_csr": (c_int, [_P, _I64, _I64, _I64, _P, _P, POINTER(_I64), _P]),
     "hpspmm_gen_uniform_degree": (c_int, [_I64, _I64, c_int32, c_int32, c_uint64, c_int32, POINTER(_P)]),
     "hpspmm_gen_erdos_renyi": (c_int, [_I64, _I64, c_double, c_uint64, c_int32, POINTER(_P)]),
@@ -313,6 +319,31 @@ class Context:
                                                   _ptr(vals_t), _ptr(perm), stream),
                     "hpspmm_csr_transpose")
 
+    def csr_to_coo_reordered(self, M, nnz, row_ptr, col_idx, vals, row_order, padding, row_out, col_out,
+                             val_out, stream=None):
+        self._check(self.lib.hpspmm_csr_to_coo_reordered(self.handle, M, nnz, _ptr(row_ptr), _ptr(col_idx),
+                                                         _ptr(vals), _ptr(row_order), padding, _ptr(row_out),
+                                                         _ptr(col_out), _ptr(val_out), stream),
+                    "hpspmm_csr_to_coo_reordered")
+
+    def csr_permute(self, M, N, nnz, row_ptr, col_idx, vals, row_order, col_new_id, row_ptr_out, col_out,
+                    val_out, stream=None):
+        self._check(self.lib.hpspmm_csr_permute(self.handle, M, N, nnz, _ptr(row_ptr), _ptr(col_idx), _ptr(vals),
+                                                _ptr(row_order), _ptr(col_new_id), _ptr(row_ptr_out),
+                                                _ptr(col_out), _ptr(val_out), stream), "hpspmm_csr_permute")
+
+    def order_rows_by_degree(self, M, row_ptr, order_out, stream=None):
+        self._check(self.lib.hpspmm_order_rows_by_degree(self.handle, M, _ptr(row_ptr), _ptr(order_out), stream),
+                    "hpspmm_order_rows_by_degree")
+
+    def invert_permutation(self, M, order, inverse_out, stream=None):
+        self._check(self.lib.hpspmm_invert_permutation(self.handle, M, _ptr(order), _ptr(inverse_out), stream),
+                    "hpspmm_invert_permutation")
+
+    def gather_rows(self, M, K, src, order, dst, stream=None):
+        self._check(self.lib.hpspmm_gather_rows_f32(self.handle, M, K, _ptr(src), _ptr(order), _ptr(dst), stream),
+                    "hpspmm_gather_rows_f32")
+
     def csr_to_coo_padded(self, M, nnz, row_ptr, col_idx, vals, padding, row_out, col_out, val_out,
                           stream=None):
         self._check(self.lib.hpspmm_csr_to_coo_padded(self.handle, M, nnz, _ptr(row_ptr),
@@ -428,6 +459,14 @@ def read_smtx(path):
     g = _P()
     _gen_check(lib, lib.hpspmm_read_smtx(path.encode(), byref(g)), "hpspmm_read_smtx")
     return _export_graph(lib, g)
+
+
+def read_row_order(path, M):
+    """Reads the reference's row order file (one line of M row ids); raises unless it is a permutation."""
+    lib = load_library()
+    out = np.empty(M, dtype=np.int32)
+    _gen_check(lib, lib.hpspmm_read_row_order(path.encode(), M, out.ctypes.data), "hpspmm_read_row_order")
+    return out
 
 
 def host_fill_uniform(count, seed, stream_id, lo, hi):

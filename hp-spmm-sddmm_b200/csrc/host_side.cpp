@@ -320,6 +320,40 @@ int hpspmm_read_smtx(const char* path, hpspmm_graph** out) {
   return HPSPMM_OK;
 }
 
+// Row order file of the reference (".cugraph_reorder", spmm/mm/spmm_common.cpp:262-267): one
+// line of M whitespace-separated row ids, the order in which rows are to be emitted.  Unlike
+// the reference this checks that the line is a permutation of 0..M-1.
+int hpspmm_read_row_order(const char* path, int64_t M, int32_t* order_out) {
+  if (!path || M < 0 || (M > 0 && !order_out)) return HPSPMM_ERR_INVALID;
+  FILE* f = fopen(path, "rb");
+  if (!f) return HPSPMM_ERR_INVALID;
+  fseek(f, 0, SEEK_END);
+  const long size = ftell(f);
+  fseek(f, 0, SEEK_SET);
+  std::vector<char> buf;
+  std::vector<char> seen;
+  try {
+    buf.resize((size_t)size + 1);
+    seen.assign((size_t)M, 0);
+  } catch (const std::bad_alloc&) {
+    fclose(f);
+    return HPSPMM_ERR_OOM;
+  }
+  const size_t got = fread(buf.data(), 1, (size_t)size, f);
+  fclose(f);
+  buf[got] = 0;
+  char* p = buf.data();
+  char* end = nullptr;
+  for (int64_t i = 0; i < M; ++i) {
+    const long v = strtol(p, &end, 10);
+    if (end == p || v < 0 || v >= M || seen[(size_t)v]) return HPSPMM_ERR_BAD_CSR;
+    seen[(size_t)v] = 1;
+    order_out[i] = (int32_t)v;
+    p = end;
+  }
+  return HPSPMM_OK;
+}
+
 int hpspmm_shard_bounds(int64_t M, const int32_t* row_ptr_host, int32_t G, int64_t* bounds) {
   if (M < 0 || !row_ptr_host || G < 1 || !bounds) return HPSPMM_ERR_INVALID;
   const int64_t nnz = row_ptr_host[M];

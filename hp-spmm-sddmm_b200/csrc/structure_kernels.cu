@@ -283,12 +283,118 @@ __global__ void chunk_cost_key_kernel(int M, int64_t n_chunks, const int* __rest
   }
 }
 
+// ---- row reordering ----------------------------------------------------------------------
+// len[i] = length of row order[i]; hits[order[i]] counts how often a row is named.
+// flag: bit 0 = an index outside [0, M), bit 1 = a row named twice.
+__global__ void ordered_row_lengths_kernel(int M, const int* __restrict__ row_ptr, const int* __restrict__ order,
+                                           int* __restrict__ len, int* __restrict__ hits, int* flag) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i <= M; i += stride) {
+    if (i == M) {
+      len[i] = 0;
+      continue;
+    }
+    const int r = order[i];
+    if (r < 0 || r >= M) {
+      len[i] = 0;
+      atomicOr(flag, 1);
+      continue;
+    }
+    len[i] = row_ptr[r + 1] - row_ptr[r];
+    if (atomicAdd(hits + r, 1) != 0) atomicOr(flag, 2);
+  }
+}
+
+// Output entry t lies in output row i = last i with new_ptr[i] <= t; it is entry
+// row_ptr[order[i]] + (t - new_ptr[i]) of the source.  row_out (optional) receives the source
+// row id, col_new_id (optional) relabels columns, entries in [nnz, padded) become (0, 0, 0).
+__global__ void permute_rows_kernel(int M, int64_t nnz, int64_t padded, const int* __restrict__ new_ptr,
+                                    const int* __restrict__ row_ptr, const int* __restrict__ order,
+                                    const int* __restrict__ col_idx, const float* __restrict__ vals,
+                                    const int* __restrict__ col_new_id, int* __restrict__ row_out,
+                                    int* __restrict__ col_out, float* __restrict__ val_out) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < padded; t += stride) {
+    if (t >= nnz) {
+      if (row_out) row_out[t] = 0;
+      if (col_out) col_out[t] = 0;
+      if (val_out) val_out[t] = 0.f;
+      continue;
+    }
+    const int i = row_of_entry(new_ptr, M, (int)t);
+    const int r = __ldg(order + i);
+    const int64_t src = (int64_t)__ldg(row_ptr + r) + (t - __ldg(new_ptr + i));
+    if (row_out) row_out[t] = r;
+    if (col_out) {
+      const int c = col_idx[src];
+      col_out[t] = col_new_id ? __ldg(col_new_id + c) : c;
+    }
+    if (val_out) val_out[t] = vals[src];
+  }
+}
+
+__global__ void degree_key_kernel(int M, const int* __restrict__ row_ptr, int* __restrict__ keys) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < M; r += stride)
+    keys[r] = 0x7fffffff - (row_ptr[r + 1] - row_ptr[r]);   // ascending key = descending degree
+}
+
+__global__ void invert_permutation_kernel(int M, const int* __restrict__ order, int* __restrict__ inv) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M; i += stride) {
+    const int r = order[i];
+    if (r >= 0 && r < M) inv[r] = (int)i;
+  }
+}
+
+// dst[i, :] = src[order[i], :], 16 bytes per thread when K % 4 == 0
+template <typename T>
+__global__ void gather_rows_kernel(int64_t M, int64_t row_elems, const T* __restrict__ src,
+                                   const int* __restrict__ order, T* __restrict__ dst) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t total = M * row_elems;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int64_t i = t / row_elems, c = t - i * row_elems;
+    dst[t] = src[(int64_t)__ldg(order + i) * row_elems + c];
+  }
+}
+
 unsigned grid_for(const hpspmm_ctx* ctx, int64_t n) {
   int64_t b = (n + kThreads - 1) / kThreads;
   const int64_t cap = (int64_t)ctx->sm_count * 32;
   if (b > cap) b = cap;
   if (b < 1) b = 1;
   return (unsigned)b;
+}
+
+// in-place exclusive scan of n ints; totals needs ceil(n / kScanTile) ints
+void exclusive_scan_inplace(hpspmm_ctx* ctx, int* data, int64_t n, int* totals, cudaStream_t s) {
+  const int64_t blocks = (n + kScanTile - 1) / kScanTile;
+  scan_block_totals_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(data, n, totals);
+  scan_single_block_kernel<<<1, kThreads, 0, s>>>(totals, blocks);
+  scan_rescan_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(data, n, totals);
+  ctx->launches += 3;
+}
+
+// new_ptr[0..M] = offsets of the rows taken in `order`; checks that order is a permutation.
+// new_ptr may be caller memory (the permuted CSR's row_ptr) or context scratch.
+int build_ordered_row_ptr(hpspmm_ctx* ctx, int64_t M, const int32_t* row_ptr, const int32_t* order,
+                          int32_t* new_ptr, int* hits, int* totals, cudaStream_t s) {
+  HPSPMM_CUDA_TRY(ctx, cudaMemsetAsync(hits, 0, (size_t)(M > 0 ? M : 1) * 4, s));
+  HPSPMM_CUDA_TRY(ctx, cudaMemsetAsync(ctx->flag, 0, sizeof(int), s));
+  ordered_row_lengths_kernel<<<grid_for(ctx, M + 1), kThreads, 0, s>>>((int)M, row_ptr, order, new_ptr, hits,
+                                                                      ctx->flag);
+  ctx->launches++;
+  exclusive_scan_inplace(ctx, new_ptr, M + 1, totals, s);
+  int flag = 0;
+  HPSPMM_CUDA_TRY(ctx, cudaMemcpyAsync(&flag, ctx->flag, sizeof(int), cudaMemcpyDeviceToHost, s));
+  HPSPMM_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+  if (flag != 0) {
+    snprintf(ctx->err, sizeof(ctx->err), "row_order is not a permutation of 0..M-1 (%s)",
+             (flag & 1) ? "index out of range" : "a row is named twice");
+    return HPSPMM_ERR_INVALID;
+  }
+  return HPSPMM_OK;
 }
 
 }  // namespace
@@ -451,6 +557,144 @@ int hpspmm_csr_transpose(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, con
   transposed_gather_kernel<<<grid_for(ctx, nnz), kThreads, 0, s>>>(nnz, row_of, vals, pin, col_idx_t,
                                                                    vals_t, perm_out);
   ctx->launches += 2;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+// scratch for the reordering entry points: [new_ptr (M+1)] [hits (M)] [scan totals]
+static int reorder_scratch(hpspmm_ctx* ctx, int64_t M, bool need_ptr, int** new_ptr, int** hits, int** totals) {
+  const size_t b_ptr = need_ptr ? align_up((size_t)(M + 1) * 4, 256) : 0;
+  const size_t b_hits = align_up((size_t)(M > 0 ? M : 1) * 4, 256);
+  const size_t b_tot = align_up((size_t)((M + 1 + kScanTile - 1) / kScanTile + 1) * 4, 256);
+  int st = hpspmm_ensure_scratch(ctx, b_ptr + b_hits + b_tot);
+  if (st != HPSPMM_OK) return st;
+  char* base = (char*)ctx->scratch;
+  if (new_ptr) *new_ptr = (int*)base;
+  *hits = (int*)(base + b_ptr);
+  *totals = (int*)(base + b_ptr + b_hits);
+  return HPSPMM_OK;
+}
+
+int hpspmm_csr_to_coo_reordered(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
+                                const int32_t* col_idx, const float* vals, const int32_t* row_order,
+                                int64_t padding, int32_t* row_out, int32_t* col_out, float* val_out,
+                                hpspmm_stream stream) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && nnz >= 0 && padding >= 0, "negative size");
+  if (M > 2147483646ll || nnz > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
+  const int64_t padded = hpspmm_padded_nnz(nnz, padding);
+  if (padded == 0) return HPSPMM_OK;
+  HPSPMM_REQUIRE(ctx, row_ptr && row_order && row_out, "null pointer");
+  HPSPMM_REQUIRE(ctx, (!col_out || col_idx) && (!val_out || vals), "missing source array");
+  hpspmm_device_guard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  int *new_ptr, *hits, *totals;
+  int st = reorder_scratch(ctx, M, true, &new_ptr, &hits, &totals);
+  if (st != HPSPMM_OK) return st;
+  st = build_ordered_row_ptr(ctx, M, row_ptr, row_order, new_ptr, hits, totals, s);
+  if (st != HPSPMM_OK) return st;
+  permute_rows_kernel<<<grid_for(ctx, padded), kThreads, 0, s>>>((int)M, nnz, padded, new_ptr, row_ptr, row_order,
+                                                                col_idx, vals, nullptr, row_out, col_out, val_out);
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+int hpspmm_csr_permute(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
+                       const int32_t* col_idx, const float* vals, const int32_t* row_order,
+                       const int32_t* col_new_id, int32_t* row_ptr_out, int32_t* col_out, float* val_out,
+                       hpspmm_stream stream) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "negative size");
+  if (M > 2147483646ll || nnz > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
+  HPSPMM_REQUIRE(ctx, row_ptr && row_order && row_ptr_out, "null pointer");
+  HPSPMM_REQUIRE(ctx, nnz == 0 || (col_idx && col_out), "null pointer");
+  HPSPMM_REQUIRE(ctx, !val_out || vals, "val_out requested without vals");
+  hpspmm_device_guard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  int *hits, *totals;
+  int st = reorder_scratch(ctx, M, false, nullptr, &hits, &totals);
+  if (st != HPSPMM_OK) return st;
+  st = build_ordered_row_ptr(ctx, M, row_ptr, row_order, row_ptr_out, hits, totals, s);
+  if (st != HPSPMM_OK || nnz == 0) return st;
+  permute_rows_kernel<<<grid_for(ctx, nnz), kThreads, 0, s>>>((int)M, nnz, nnz, row_ptr_out, row_ptr, row_order,
+                                                             col_idx, vals, col_new_id, nullptr, col_out, val_out);
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+int hpspmm_order_rows_by_degree(hpspmm_ctx* ctx, int64_t M, const int32_t* row_ptr, int32_t* order_out,
+                                hpspmm_stream stream) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0, "negative size");
+  if (M > 2147483646ll) return HPSPMM_ERR_UNSUPPORTED;
+  if (M == 0) return HPSPMM_OK;
+  HPSPMM_REQUIRE(ctx, row_ptr && order_out, "null pointer");
+  hpspmm_device_guard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int n_tiles = (int)((M + kTile - 1) / kTile);
+  const int64_t hist_n = (int64_t)256 * n_tiles;
+  const int64_t scan_blocks = (hist_n + kScanTile - 1) / kScanTile;
+  const size_t b_arr = align_up((size_t)M * 4, 256);
+  const size_t b_hist = align_up((size_t)hist_n * 4, 256);
+  const size_t b_tot = align_up((size_t)scan_blocks * 4, 256);
+  int st = hpspmm_ensure_scratch(ctx, 3 * b_arr + b_hist + b_tot);
+  if (st != HPSPMM_OK) return st;
+  char* base = (char*)ctx->scratch;
+  int* keys[2] = {(int*)base, (int*)(base + b_arr)};
+  int* pay_tmp = (int*)(base + 2 * b_arr);
+  int* hist = (int*)(base + 3 * b_arr);
+  int* totals = (int*)(base + 3 * b_arr + b_hist);
+  degree_key_kernel<<<grid_for(ctx, M), kThreads, 0, s>>>((int)M, row_ptr, keys[0]);
+  ctx->launches++;
+  // four stable 8-bit passes; payloads alternate between pay_tmp and order_out and end in order_out
+  const int* pin = nullptr;
+  for (int p = 0; p < 4; ++p) {
+    const int* kin = keys[p & 1];
+    int* kout = keys[(p & 1) ^ 1];
+    int* pout = (p & 1) ? order_out : pay_tmp;
+    radix_hist_kernel<<<n_tiles, kThreads, 0, s>>>(kin, M, 8 * p, n_tiles, hist);
+    scan_block_totals_kernel<<<(unsigned)scan_blocks, kThreads, 0, s>>>(hist, hist_n, totals);
+    scan_single_block_kernel<<<1, kThreads, 0, s>>>(totals, scan_blocks);
+    scan_rescan_kernel<<<(unsigned)scan_blocks, kThreads, 0, s>>>(hist, hist_n, totals);
+    radix_scatter_kernel<<<n_tiles, kThreads, 0, s>>>(kin, pin, M, 8 * p, n_tiles, hist, kout, pout);
+    ctx->launches += 5;
+    pin = pout;
+  }
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+int hpspmm_invert_permutation(hpspmm_ctx* ctx, int64_t M, const int32_t* order, int32_t* inverse_out,
+                              hpspmm_stream stream) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0, "negative size");
+  if (M > 2147483646ll) return HPSPMM_ERR_UNSUPPORTED;
+  if (M == 0) return HPSPMM_OK;
+  HPSPMM_REQUIRE(ctx, order && inverse_out, "null pointer");
+  hpspmm_device_guard guard(ctx->device);
+  invert_permutation_kernel<<<grid_for(ctx, M), kThreads, 0, (cudaStream_t)stream>>>((int)M, order, inverse_out);
+  ctx->launches++;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
+int hpspmm_gather_rows_f32(hpspmm_ctx* ctx, int64_t M, int64_t K, const float* src, const int32_t* order,
+                           float* dst, hpspmm_stream stream) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && K >= 1, "bad size");
+  if (M == 0) return HPSPMM_OK;
+  HPSPMM_REQUIRE(ctx, src && order && dst && src != dst, "null pointer or in-place gather");
+  hpspmm_device_guard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool vec = (K % 4 == 0) && (((uintptr_t)src | (uintptr_t)dst) % 16 == 0);
+  if (vec)
+    gather_rows_kernel<float4><<<grid_for(ctx, M * (K / 4)), kThreads, 0, s>>>(
+        M, K / 4, reinterpret_cast<const float4*>(src), order, reinterpret_cast<float4*>(dst));
+  else
+    gather_rows_kernel<float><<<grid_for(ctx, M * K), kThreads, 0, s>>>(M, K, src, order, dst);
+  ctx->launches++;
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;
 }

@@ -270,6 +270,42 @@ HPSPMM_API int hpspmm_csr_to_coo_padded(hpspmm_ctx* ctx, int64_t M, int64_t nnz,
                                         const float* vals, int64_t padding, int32_t* row_out,
                                         int32_t* col_out, float* val_out, hpspmm_stream stream);
 
+/* ---- row reordering (device) ---------------------------------------------------------------
+ * The reference reorders by emitting COO rows in the order an offline permutation file names,
+ * each entry keeping its original row id (get_coo_mat_from_smtx_reorder,
+ * spmm/mm/spmm_common.cpp:237-296).  row_order[i] = source row emitted i-th; it must be a
+ * permutation of 0..M-1 (checked on the device; HPSPMM_ERR_INVALID otherwise).  These calls
+ * are set-up work: each synchronises the stream once.
+ *
+ * csr_to_coo_reordered: that emission, padded like hpspmm_csr_to_coo_padded; feed the arrays
+ *   to hpspmm_spmm_coo_f32.  Integer outputs are bit-exact.
+ * csr_permute: the CSR form A' = P * A * Q: row i of A' is row row_order[i] of A, and column c
+ *   is relabelled col_new_id[c] when col_new_id is given (NULL keeps column ids).  For a
+ *   symmetric reordering pass the inverse of row_order.  Entries keep their order inside a
+ *   row, so relabelled columns are in general not ascending.  No counterpart in the
+ *   reference, whose CSR entry has no reordered form.
+ * order_rows_by_degree: row ids by descending row length, ties by ascending id (a stable
+ *   radix sort).  The reference takes its order from an offline tool; this is the built-in one.
+ * invert_permutation: inverse_out[order[i]] = i.
+ * gather_rows_f32: dst[i, :] = src[order[i], :] for an M x K row-major matrix (dst != src);
+ *   carries B or C into and out of a reordered numbering. */
+HPSPMM_API int hpspmm_csr_to_coo_reordered(hpspmm_ctx* ctx, int64_t M, int64_t nnz,
+                                           const int32_t* row_ptr, const int32_t* col_idx,
+                                           const float* vals, const int32_t* row_order,
+                                           int64_t padding, int32_t* row_out, int32_t* col_out,
+                                           float* val_out, hpspmm_stream stream);
+HPSPMM_API int hpspmm_csr_permute(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz,
+                                  const int32_t* row_ptr, const int32_t* col_idx,
+                                  const float* vals, const int32_t* row_order,
+                                  const int32_t* col_new_id, int32_t* row_ptr_out,
+                                  int32_t* col_out, float* val_out, hpspmm_stream stream);
+HPSPMM_API int hpspmm_order_rows_by_degree(hpspmm_ctx* ctx, int64_t M, const int32_t* row_ptr,
+                                           int32_t* order_out, hpspmm_stream stream);
+HPSPMM_API int hpspmm_invert_permutation(hpspmm_ctx* ctx, int64_t M, const int32_t* order,
+                                         int32_t* inverse_out, hpspmm_stream stream);
+HPSPMM_API int hpspmm_gather_rows_f32(hpspmm_ctx* ctx, int64_t M, int64_t K, const float* src,
+                                      const int32_t* order, float* dst, hpspmm_stream stream);
+
 /* ---- validation ------------------------------------------------------------------------
  * Checks row_ptr[0] == 0, monotone row_ptr, row_ptr[M] == nnz, 0 <= col < N on the device;
  * synchronises; returns HPSPMM_ERR_BAD_CSR and the first offending position found.
@@ -303,6 +339,9 @@ HPSPMM_API int hpspmm_gen_free(hpspmm_graph* g);
  * One-pass reader of the reference's text format (spmm/mm/spmm_common.cpp:125-174):
  * line 1 "rows,cols,nnz", line 2 rows+1 offsets, line 3 nnz column ids; values are 1.0. */
 HPSPMM_API int hpspmm_read_smtx(const char* path, hpspmm_graph** out);
+/* Row order file of the reference (".cugraph_reorder", spmm/mm/spmm_common.cpp:262-267): one
+ * line of M row ids.  Fills order_out[M]; HPSPMM_ERR_BAD_CSR unless it is a permutation. */
+HPSPMM_API int hpspmm_read_row_order(const char* path, int64_t M, int32_t* order_out);
 
 /* ---- host side: multi-GPU row sharding ---------------------------------------------------------
  * nnz-balanced contiguous row blocks: bounds[g] = first row r with row_ptr[r] >= g*nnz/G;

@@ -156,3 +156,19 @@ def test_torch_front_end_registers_and_has_no_cpu_path(pkg):
             assert ops.layer_backward_weights(torch.empty(7, 32), H, -1).shape == (9,)
     finally:
         del ops._layers[-1]
+
+
+def test_row_order_reader(pkg, tmp_path):
+    """One line of M row ids (the reference's .cugraph_reorder file); anything but a permutation is refused."""
+    rng = np.random.default_rng(5)
+    order = rng.permutation(1000).astype(np.int32)
+    good = tmp_path / "g.cugraph_reorder"
+    good.write_text(" ".join(str(int(x)) for x in order) + "\n")
+    assert np.array_equal(pkg.read_row_order(str(good), 1000), order)
+    for name, text in (("dup", "0 1 1 3"), ("range", "0 1 2 4"), ("short", "0 1 2"), ("neg", "0 -1 2 3")):
+        bad = tmp_path / name
+        bad.write_text(text + "\n")
+        with pytest.raises(pkg.HpspmmError):
+            pkg.read_row_order(str(bad), 4)
+    with pytest.raises(pkg.HpspmmError):
+        pkg.read_row_order(str(tmp_path / "missing"), 4)
