@@ -97,6 +97,7 @@ PROTOTYPES = {
     "hpspmm_sddmm_csr_f32": (c_int, [_P, _P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P,
                                      POINTER(Opts), _P]),
     "hpspmm_csr_transpose": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "hpspmm_plan_tables": (c_int, [_P, POINTER(_P), POINTER(_P), POINTER(_P)]),
     "hpspmm_layer_create": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _I64, _P, POINTER(_P)]),
     "hpspmm_layer_destroy": (c_int, [_P, _P]),
     "hpspmm_layer_info": (c_int, [_P, POINTER(_I64), POINTER(_I64), POINTER(_I64), POINTER(_I64),
@@ -287,6 +288,12 @@ class Context:
                     "hpspmm_plan_info")
         return {"n_chunks": a.value, "n_split_chunks": b.value, "chunk_nnz": c.value,
                 "scratch_bytes": d.value}
+
+    def plan_tables(self, plan):
+        """Device addresses of chunk_start, chunk_row, chunk_order."""
+        a, b, c = _P(), _P(), _P()
+        self._check(self.lib.hpspmm_plan_tables(plan, byref(a), byref(b), byref(c)), "hpspmm_plan_tables")
+        return a.value, b.value, c.value
 
     def spmm_csr(self, M, N, K, nnz, row_ptr, col_idx, vals, B, C, plan=None, opts=None, stream=None):
         self._check(self.lib.hpspmm_spmm_csr_f32(self.handle, plan, M, N, K, nnz, _ptr(row_ptr),

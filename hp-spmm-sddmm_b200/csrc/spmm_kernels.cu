@@ -994,6 +994,15 @@ int hpspmm_plan_info(const hpspmm_plan* plan, int64_t* n_chunks, int64_t* n_spli
   return HPSPMM_OK;
 }
 
+int hpspmm_plan_tables(const hpspmm_plan* plan, const int32_t** chunk_start, const int32_t** chunk_row,
+                       const int32_t** chunk_order) {
+  if (!plan) return HPSPMM_ERR_INVALID;
+  if (chunk_start) *chunk_start = plan->chunk_start;
+  if (chunk_row) *chunk_row = plan->chunk_row;
+  if (chunk_order) *chunk_order = plan->chunk_order;
+  return HPSPMM_OK;
+}
+
 int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int64_t N, int64_t K,
                         int64_t nnz, const int32_t* row_ptr, const int32_t* col_idx,
                         const float* vals, const float* B, float* C, const hpspmm_opts* opts,

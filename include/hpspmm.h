@@ -149,6 +149,11 @@ HPSPMM_API int hpspmm_plan_destroy(hpspmm_ctx* ctx, hpspmm_plan* plan);
 HPSPMM_API int hpspmm_plan_info(const hpspmm_plan* plan, int64_t* n_chunks,
                                 int64_t* n_split_chunks, int64_t* chunk_nnz,
                                 int64_t* scratch_bytes);
+/* Device pointers to the plan's tables, for inspection: chunk_start[n_chunks + 1] (first
+ * entry of every chunk), chunk_row[n_chunks] (row holding that entry), chunk_order[n_chunks]
+ * (the chunk ids in the order in which warps take them: a permutation of 0..n_chunks-1). */
+HPSPMM_API int hpspmm_plan_tables(const hpspmm_plan* plan, const int32_t** chunk_start,
+                                  const int32_t** chunk_row, const int32_t** chunk_order);
 
 /* The same product for callers that cannot allocate device memory when they need it.
  * (No counterpart in the reference, whose entry points allocate nothing because its

@@ -186,3 +186,31 @@ def test_fill_factories_match_host(gpu_ctx, pkg):
     gpu_ctx.fill(d, n, 2.5)
     assert np.all(d.to_host() == 2.5)
     d.free()
+
+
+@pytest.mark.parametrize("with_cols", [False, True])
+def test_plan_tables_tile_the_matrix_and_schedule_every_chunk_once(gpu_ctx, pkg, with_cols):
+    ctx = gpu_ctx
+    g = pkg.gen_rmat(13, 16, seed=12)
+    M, N, nnz = g["M"], g["N"], g["nnz"]
+    d_rp, d_ci = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"])
+    plan = ctx.plan_create(M, nnz, d_rp, 32, N=N, col_idx=d_ci if with_cols else None)
+    n = ctx.plan_info(plan)["n_chunks"]
+    p_start, p_row, p_order = ctx.plan_tables(plan)
+
+    def read(ptr, count):
+        out = np.empty(count, dtype=np.int32)
+        ctx.memcpy_d2h(out, ptr)
+        ctx.stream_sync()
+        return out
+
+    start, row, order = read(p_start, n + 1), read(p_row, n), read(p_order, n)
+    assert start[0] == 0 and start[-1] == nnz and np.all(np.diff(start) >= 0)
+    assert np.all(np.diff(start) <= 2 * 128)                       # nominal size 128; snapping moves a cut by < 128
+    rp = g["row_ptr"]
+    nonempty = np.diff(start) > 0
+    assert np.all(rp[row[nonempty]] <= start[:-1][nonempty]) and np.all(start[:-1][nonempty] < rp[row[nonempty] + 1])
+    assert np.array_equal(np.sort(order), np.arange(n, dtype=np.int32))
+    ctx.plan_destroy(plan)
+    d_rp.free()
+    d_ci.free()
