@@ -39,8 +39,8 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the K = 128 product kernel on
 # the N = 1 workload, from the ncu capture summarised in profiles/spmm_warp_kernel_rmat20.md
-# (1663.8 MB read + 616.2 MB written; the same full-size workload, about 1 GB on the device).
-NCU_TRAFFIC_BYTES_K128 = 2279968632
+# (1368.2 MB read + 596.2 MB written; the same full-size workload, about 1 GB on the device).
+NCU_TRAFFIC_BYTES_K128 = 1964432552
 
 
 def load_peak():
@@ -175,6 +175,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--only-k", type=int, default=0, help="profiling aid: run a single K")
+    ap.add_argument("--no-compare", action="store_true",
+                    help="skip the off-path cuSPARSE column (torch.sparse CSR product, N = 1 only)")
     ap.add_argument("--b-sharded", action="store_true",
                     help="B is produced row-sharded (a GNN layer's output): every step all-gathers it "
                          "with NCCL into each GPU's own HBM before the local product")
@@ -376,6 +378,34 @@ def main():
                "kind": "port", "sample": "full workload, all K, 1 warm-up + 2 timed passes",
                "ms_per_pass": dt * 1e3}
 
+    # ---- off-path comparison column: cuSPARSE CSR SpMM through torch.sparse (library code, N = 1 only),
+    # the baseline the reference's own driver prints beside its kernels (test/test_all.cpp:61-87)
+    compare = None
+    if rank == 0 and n_gpus == 1 and not args.no_compare:
+        compare = {"cusparse_csr_ms": {}, "note": "torch.sparse CSR @ dense (cuSPARSE SpMM), same operands, "
+                   "3 warm-up + 10 timed launches, CUDA events"}
+        try:
+            A_t = torch.sparse_csr_tensor(t_rp.to(torch.int64), t_ci.to(torch.int64), t_v, size=(M_l, N))
+            for K in ks:
+                for _ in range(3):
+                    out = A_t @ Bs[K]
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(10):
+                    out = A_t @ Bs[K]
+                b.record()
+                torch.cuda.synchronize()
+                compare["cusparse_csr_ms"][str(K)] = a.elapsed_time(b) / 10
+                torch.testing.assert_close(out, Cs[K], rtol=1e-3, atol=1e-3)
+                del out
+            del A_t
+        except Exception as exc:   # a library column must never fail the bench
+            compare["error"] = "%s: %s" % (type(exc).__name__, str(exc)[:200])
+        rec = os.path.join(ROOT, "tests", "golden", "reference_timings.json")
+        if os.path.exists(rec):
+            with open(rec) as fh:
+                compare["reference_kernels_recorded"] = json.load(fh)
+
     if rank == 0:
         line = {
             "metric": "SpMM GFLOPS (2*nnz*K/s), K=32+64+128", "value": value, "unit": "GFLOPS",
@@ -390,6 +420,7 @@ def main():
                        "b": "all-gathered per step (NCCL)" if b_sharded else "replicated",
                        "parallelism": "row-shard x%d" % n_gpus},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "comparisons": compare,
             "clocks": clocks,
         }
         print(json.dumps(line))
