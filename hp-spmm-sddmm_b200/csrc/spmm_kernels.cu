@@ -653,6 +653,131 @@ carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
 }
 
 // ---- COO, accumulate -------------------------------------------------------------------
+// ---- COO warp kernel: K = 4 * W in {32, 64, 128} --------------------------------------------
+// C += A * B from (row, col, val) triples in any order; zero-valued entries (the padding) are
+// skipped.  Same machinery as the CSR warp kernel: one warp per S consecutive triples, G = 32 / W
+// lane groups that each gather a whole row of B per step, tiles of 32 triples staged global ->
+// shared with cp.async two tiles ahead, U steps of gathers in flight, an unrolled path for tiles
+// that lie inside one row.  Row boundaries come from the staged row ids (one ballot per tile)
+// instead of row_ptr; every run of equal row ids ends in one cross-group reduction and one
+// 16-byte vector reduction per lane of group 0 into C.
+template <int W, int U, int BT>
+__global__ void __launch_bounds__(BT, 16)
+spmm_coo_warp_kernel(int64_t nnz, int S, const int* __restrict__ row_idx, const int* __restrict__ col_idx,
+                     const float* __restrict__ vals, const float* __restrict__ B, float* __restrict__ C) {
+  constexpr int K = 4 * W;
+  constexpr int G = 32 / W;
+  constexpr int T = 32;
+  constexpr int BATCH = U * G;
+  constexpr int STAGES = 2;
+  static_assert(BATCH <= T && T % BATCH == 0, "batch must tile the staged tile");
+  __shared__ int2 cv_tiles[BT / 32][STAGES][T];
+  __shared__ int row_tiles[BT / 32][STAGES][T];
+
+  const int lane = threadIdx.x & 31;
+  const int g = lane / W, l = lane % W;
+  const int64_t worker = ((int64_t)blockIdx.x * BT + threadIdx.x) >> 5;
+  const int64_t n0 = worker * S;
+  if (n0 >= nnz) return;
+  const int64_t n1 = min(nnz, n0 + (int64_t)S);
+  int2(*cv)[T] = cv_tiles[threadIdx.x >> 5];
+  int(*rw)[T] = row_tiles[threadIdx.x >> 5];
+
+  auto stage_tile = [&](int stage, int64_t base) {
+    const int64_t j = base + lane;
+    if (j < n1) {
+      cp_async_4(&cv[stage][lane].x, col_idx + j);
+      cp_async_4(&cv[stage][lane].y, vals + j);
+      cp_async_4(&rw[stage][lane], row_idx + j);
+    } else {
+      cv[stage][lane] = make_int2(0, 0);   // past the chunk: column 0, value 0 (skipped)
+      rw[stage][lane] = -1;
+    }
+    cp_async_commit();
+  };
+  stage_tile(0, n0);
+  stage_tile(1, n0 + T);
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* Bl = B + l * 4;
+  int cur_row = -1;   // row of the run being accumulated
+
+  auto flush = [&]() {
+    if (cur_row >= 0) {
+      const float4 t = reduce_groups<W>(acc);
+      if (g == 0) red_add_v4(C + (int64_t)cur_row * K + l * 4, t);
+    }
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  };
+
+  int stage = 0;
+  for (int64_t base = n0; base < n1; base += T) {
+    cp_async_wait<STAGES - 1>();
+    __syncwarp();
+    // bit e: triple e of the tile starts a new run (its row differs from its predecessor's);
+    // triples past the chunk carry row -1 and never match, which ends the last run
+    const int my_row = rw[stage][lane];
+    const int prev_row = lane == 0 ? cur_row : rw[stage][lane - 1];
+    unsigned bnd = __ballot_sync(0xffffffffu, my_row != prev_row);
+    const int2* tile = &cv[stage][g];
+    if (bnd == 0u) {
+      // the whole tile continues the current run
+#pragma unroll
+      for (int s0 = 0; s0 < T / G; s0 += U) {
+        float4 b[U];
+        float v[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+          const int2 e = tile[(s0 + i) * G];
+          v[i] = __int_as_float(e.y);
+          b[i] = ld_gather<false>(Bl + (int64_t)e.x * K, 0ull);
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i)
+          if (v[i] != 0.f) fma4(acc, v[i], b[i]);
+      }
+    } else {
+      const int limit = (int)min((int64_t)T, n1 - base);   // triples of this tile inside the chunk
+#pragma unroll 1
+      for (int u0 = 0; u0 < T; u0 += BATCH) {
+        if (u0 >= limit) break;
+        float4 b[U];
+        float v[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+          const int2 e = tile[u0 + i * G];
+          v[i] = __int_as_float(e.y);
+          b[i] = ld_gather<false>(Bl + (int64_t)e.x * K, 0ull);
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+          const int lo = u0 + i * G;
+          const int hi = min(lo + G, limit);
+          const int mine = lo + g;
+          int cur = lo;
+          // warp-uniform: runs that start inside this step
+          unsigned m = hi > lo ? (bnd >> lo) & ((1u << (hi - lo)) - 1u) : 0u;
+          while (m) {
+            const int p = lo + __ffs(m) - 1;
+            m &= m - 1;
+            if (mine >= cur && mine < p && v[i] != 0.f) fma4(acc, v[i], b[i]);
+            flush();
+            cur_row = rw[stage][p];
+            cur = p;
+          }
+          if (mine >= cur && mine < hi && v[i] != 0.f) fma4(acc, v[i], b[i]);
+        }
+      }
+    }
+    // the last triple's row carries into the next tile's first comparison
+    __syncwarp();
+    stage_tile(stage, base + STAGES * T);
+    stage ^= 1;
+  }
+  cp_async_wait<0>();
+  flush();
+}
+
 // C += A * B from (row, col, val) triples in any order; zero-valued padding is skipped.
 // One warp per run of S entries; a lane owns columns (s*32 + lane)*VEC of a 128*VEC-wide
 // column block.  Partial sums leave through vector reductions on every row change.
@@ -1207,6 +1332,23 @@ int hpspmm_spmm_coo_f32(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_
   const int64_t blocks = (n_workers + kBlockThreads / 32 - 1) / (kBlockThreads / 32);
   if (blocks > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
+  if (K == 32 || K == 64 || K == 128) {
+    int32_t Sw = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
+    Sw = (Sw + 31) / 32 * 32;
+    constexpr int BT = 64;
+    const int64_t n_w = (nnz_padded + Sw - 1) / Sw;
+    const int64_t nb = (n_w + BT / 32 - 1) / (BT / 32);
+    if (nb > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
+    if (K == 32)
+      spmm_coo_warp_kernel<8, 4, BT><<<(unsigned)nb, BT, 0, s>>>(nnz_padded, Sw, row_idx, col_idx, vals, B, C);
+    else if (K == 64)
+      spmm_coo_warp_kernel<16, 4, BT><<<(unsigned)nb, BT, 0, s>>>(nnz_padded, Sw, row_idx, col_idx, vals, B, C);
+    else
+      spmm_coo_warp_kernel<32, 4, BT><<<(unsigned)nb, BT, 0, s>>>(nnz_padded, Sw, row_idx, col_idx, vals, B, C);
+    ctx->launches++;
+    HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+    return HPSPMM_OK;
+  }
   if ((K & 3) == 0) {
     // narrow K keeps one column slab per lane so no lane idles on dead slabs
     if (K <= 128) {
