@@ -45,6 +45,7 @@ struct hpspmm_plan {
   int32_t* chunk_order;  // chunk ids, most rows first: the order in which warps take chunks
   int32_t* carry_row;
   float* carry_val;
+  int32_t* run_counter;  // one per chunk, zero between launches: pieces of a split row that have finished
   size_t bytes;
 };
 

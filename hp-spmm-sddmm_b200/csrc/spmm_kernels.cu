@@ -280,14 +280,71 @@ __device__ __forceinline__ float4 reduce_groups(float4 a) {
   return a;
 }
 
-template <int W, int U, int MINB, bool HINT, int BT>
+// In-kernel fix-up of one split row.  A row longer than S is cut at multiples of S only, so its pieces
+// are the chunks first = row_ptr[r] / S .. last = (row_ptr[r+1] - 1) / S: all but the last hand a carry
+// on, the last stores the row.  Every piece bumps the row's counter when its own part is visible
+// device-wide; whoever bumps it last adds the carries, in chunk order, to the stored row.  The sum does
+// not depend on who that is, so results stay bit-reproducible.  No piece ever waits.  Kept out of line
+// so that its registers do not weigh on the gather loop of the caller.
+template <int W>
+__device__ __noinline__ void settle_split_row(int r, int r_end, int S, const int* __restrict__ row_ptr,
+                                              const float* __restrict__ carry_val, float* __restrict__ C,
+                                              int* __restrict__ run_counter) {
+  constexpr int K = 4 * W;
+  constexpr int G = 32 / W;
+  const int lane = threadIdx.x & 31;
+  const int g = lane / W, l = lane % W;
+  const int first = __ldg(row_ptr + r) / S;
+  const int last = (r_end - 1) / S;
+  int seen = 0;
+  if (lane == 0) seen = atomicAdd(run_counter + first, 1);
+  seen = __shfl_sync(0xffffffffu, seen, 0);
+  if (seen != last - first) return;
+  __threadfence();
+  const float* src = carry_val + (int64_t)first * K + l * 4;
+  const int len = last - first;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  int i = g;
+  for (; i + 7 * G < len; i += 8 * G) {
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (int64_t)(i + u * G) * K));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      sum.x += v[u].x;
+      sum.y += v[u].y;
+      sum.z += v[u].z;
+      sum.w += v[u].w;
+    }
+  }
+  for (; i < len; i += G) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (int64_t)i * K));
+    sum.x += v.x;
+    sum.y += v.y;
+    sum.z += v.z;
+    sum.w += v.w;
+  }
+  sum = reduce_groups<W>(sum);
+  if (g == 0) {
+    float4* out = reinterpret_cast<float4*>(C + (int64_t)r * K + l * 4);
+    float4 o = __ldcg(out);
+    o.x += sum.x;
+    o.y += sum.y;
+    o.z += sum.z;
+    o.w += sum.w;
+    st_stream(reinterpret_cast<float*>(out), o);
+  }
+  if (lane == 0) run_counter[first] = 0;   // ready for the next launch
+}
+
+template <int W, int U, int MINB, bool HINT, int BT, bool SETTLE>
 __global__ void __launch_bounds__(BT, MINB)
 spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict__ row_ptr,
                  const int* __restrict__ col_idx, const float* __restrict__ vals,
                  const float* __restrict__ B, float* __restrict__ C,
                  const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
                  int* __restrict__ carry_row, float* __restrict__ carry_val,
-                 const int* __restrict__ chunk_order) {
+                 const int* __restrict__ chunk_order, int S, int* __restrict__ run_counter) {
   constexpr int K = 4 * W;
   constexpr int G = 32 / W;      // lane groups = entries gathered per warp instruction
   constexpr int T = 32;          // entries per staged tile
@@ -420,13 +477,27 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   cp_async_wait<0>();
 
   const float4 t = reduce_groups<W>(acc);
-  if (row_end == n1) {
+  const bool hands_on = row_end != n1;   // the chunk ends inside `row`
+  if (!hands_on) {
     if (g == 0) st_stream(C + (int64_t)row * K + l * 4, t);
-    if (lane == 0) carry_row[chunk] = -1;
   } else {
     if (g == 0) *reinterpret_cast<float4*>(carry_val + (int64_t)chunk * K + l * 4) = t;
-    if (lane == 0) carry_row[chunk] = row;
   }
+  if (!SETTLE) {
+    // a separate kernel adds the carries
+    if (lane == 0) carry_row[chunk] = hands_on ? row : -1;
+    return;
+  }
+
+  // the pieces of a split row settle it among themselves (settle_split_row)
+  const int r0 = __ldg(chunk_row + chunk);
+  const int r0_start = __ldg(row_ptr + r0), r0_end = __ldg(row_ptr + r0 + 1);
+  const bool stores_split_row = r0_start < n0 && r0_end <= n1;   // began in an earlier chunk, ends here
+  if (!hands_on && !stores_split_row) return;
+  __threadfence();
+  __syncwarp();   // every lane's part is visible before lane 0 bumps a counter
+  if (stores_split_row) settle_split_row<W>(r0, r0_end, S, row_ptr, carry_val, C, run_counter);
+  if (hands_on) settle_split_row<W>(row, row_end, S, row_ptr, carry_val, C, run_counter);
 }
 
 // ---- generic kernel: any K -------------------------------------------------------------
@@ -899,7 +970,7 @@ template <int W, int U, int MINB, int BT = kBlockThreads>
 int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* row_ptr,
                 const int32_t* col_idx, const float* vals, const float* B, float* C,
                 const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
-                float* carry_val, const int32_t* chunk_order, cudaStream_t stream) {
+                float* carry_val, const int32_t* chunk_order, int S, int* run_counter, cudaStream_t stream) {
   const int chunks_per_block = BT / 32;
   const int n_chunk_blocks = (n_chunks + chunks_per_block - 1) / chunks_per_block;
   int n_zero_blocks = (M + BT - 1) / BT;
@@ -907,14 +978,16 @@ int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* 
   if (n_zero_blocks > cap) n_zero_blocks = cap;
   const unsigned grid = (unsigned)(n_chunk_blocks + n_zero_blocks);
   if (grid == 0) return HPSPMM_OK;
-  if (hint)
-    spmm_warp_kernel<W, U, MINB, true, BT><<<grid, BT, 0, stream>>>(
-        M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
-        carry_row, carry_val, chunk_order);
-  else
-    spmm_warp_kernel<W, U, MINB, false, BT><<<grid, BT, 0, stream>>>(
-        M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
-        carry_row, carry_val, chunk_order);
+#define HPSPMM_LAUNCH_WARP(H, ST)                                                               \
+  spmm_warp_kernel<W, U, MINB, H, BT, ST><<<grid, BT, 0, stream>>>(                                \
+      M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, \
+      carry_val, chunk_order, S, run_counter)
+  if (run_counter != nullptr) {
+    if (hint) HPSPMM_LAUNCH_WARP(true, true); else HPSPMM_LAUNCH_WARP(false, true);
+  } else {
+    if (hint) HPSPMM_LAUNCH_WARP(true, false); else HPSPMM_LAUNCH_WARP(false, false);
+  }
+#undef HPSPMM_LAUNCH_WARP
   ctx->launches++;
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;
@@ -1001,14 +1074,20 @@ int check_spmm_args(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nn
 int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, int64_t n_chunks,
              const int32_t* row_ptr, const int32_t* col_idx, const float* vals, const float* B,
              float* C, const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
-             float* carry_val, const int32_t* chunk_order, bool need_fixup, cudaStream_t stream) {
+             float* carry_val, const int32_t* chunk_order, bool need_fixup, cudaStream_t stream,
+             int S = 0, int* run_counter = nullptr) {
   int st;
   const int m = (int)M, nc = (int)n_chunks;
+  // With a counter array the warp kernels add the carries themselves.  Measured on the R-MAT bench graph
+  // against the separate fix-up kernel: -6 % at K = 128, -2 % at K = 64, but +7 % at K = 32, where chunks
+  // are short and the device-wide fence every piece of a split row takes weighs more than the launch saved.
+  const bool in_kernel_fixup = !rowsplit && run_counter != nullptr && (K == 64 || K == 128);
+  if (!in_kernel_fixup) run_counter = nullptr;
   // Tuning on B200 (R-MAT scale 20): 64-thread blocks, U = 4 gather steps in flight per lane and
   // at most 51 registers (20 blocks per SM) beat 128/256-thread blocks, U = 2/8/16 and the
   // 32/40/64/80-register builds at every K.
 #define HPSPMM_ARGS ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, stream
-#define HPSPMM_WARGS ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, chunk_order, stream
+#define HPSPMM_WARGS ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, chunk_order, S, run_counter, stream
   if (K == 32) {
     st = rowsplit ? launch_balanced<8, 1, 8, 4>(HPSPMM_ARGS) : launch_warp<8, 4, 20, 64>(HPSPMM_WARGS);
   } else if (K == 64) {
@@ -1025,7 +1104,7 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
     st = launch_generic<1>(ctx, rowsplit, m, (int)K, nc, row_ptr, col_idx, vals, B, C, chunk_start,
                            chunk_row, carry_row, carry_val, chunk_order, stream);
   if (st != HPSPMM_OK) return st;
-  if (!rowsplit && need_fixup && n_chunks > 0) {
+  if (!rowsplit && need_fixup && n_chunks > 0 && !in_kernel_fixup) {
     const unsigned blocks = (unsigned)((n_chunks + kBlockThreads - 1) / kBlockThreads);
     carry_fixup_kernel<<<blocks, kBlockThreads, 0, stream>>>((int)K, nc, carry_row, carry_val, C);
     ctx->launches++;
@@ -1063,8 +1142,9 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const
   const size_t b_crow = align_up((size_t)(p->n_chunks + 1) * 4, 256);
   const size_t b_cval = align_up((size_t)(p->n_chunks + 1) * (size_t)max_K * 4, 256);
   const size_t b_order = align_up((size_t)(p->n_chunks + 1) * 4, 256);
+  const size_t b_count = align_up((size_t)(p->n_chunks + 1) * 4, 256);
   const size_t b_sort = hpspmm_order_scratch_bytes(p->n_chunks);   // only needed while building
-  p->bytes = b_start + b_row + b_crow + b_cval + b_order + b_sort;
+  p->bytes = b_start + b_row + b_crow + b_cval + b_order + b_count + b_sort;
   char* base = nullptr;
   cudaError_t e = cudaMalloc((void**)&base, p->bytes);
   if (e != cudaSuccess) {
@@ -1076,11 +1156,13 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const
   p->carry_row = (int32_t*)(base + b_start + b_row);
   p->carry_val = (float*)(base + b_start + b_row + b_crow);
   p->chunk_order = (int32_t*)(base + b_start + b_row + b_crow + b_cval);
-  void* sort_scratch = base + b_start + b_row + b_crow + b_cval + b_order;
+  p->run_counter = (int32_t*)(base + b_start + b_row + b_crow + b_cval + b_order);
+  void* sort_scratch = base + b_start + b_row + b_crow + b_cval + b_order + b_count;
   cudaStream_t s = (cudaStream_t)stream;
   int st = HPSPMM_OK;
   int split = 0;
   e = cudaMemsetAsync(ctx->flag, 0, sizeof(int), s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(p->run_counter, 0, b_count, s);
   if (e == cudaSuccess && M > 0)
     st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, p->n_chunks, p->chunk_start,
                                    p->chunk_row, ctx->flag, s);
@@ -1151,7 +1233,7 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
     HPSPMM_REQUIRE(ctx, plan->device == ctx->device, "plan built on another device");
     return run_spmm(ctx, hint, false, M, K, plan->n_chunks, row_ptr, col_idx, vals, B, C,
                     plan->chunk_start, plan->chunk_row, plan->carry_row, plan->carry_val,
-                    plan->chunk_order, plan->n_split_chunks > 0, s);
+                    plan->chunk_order, plan->n_split_chunks > 0, s, plan->chunk_nnz, plan->run_counter);
   }
   int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
   S = (S + 31) / 32 * 32;
