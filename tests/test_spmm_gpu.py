@@ -214,3 +214,43 @@ def test_plan_tables_tile_the_matrix_and_schedule_every_chunk_once(gpu_ctx, pkg,
     ctx.plan_destroy(plan)
     d_rp.free()
     d_ci.free()
+
+
+@pytest.mark.parametrize("K", [64, 128])
+@pytest.mark.parametrize("chunk", [32, 256])
+def test_split_rows_settled_inside_the_kernel_on_repeated_calls(gpu_ctx, pkg, oracle, K, chunk):
+    """With a plan, K = 64/128 add the carries of split rows inside the product kernel, through per-row
+    counters that must be back at zero after every launch: three calls on one plan, rows of 1 to 20,000
+    entries (up to 625 pieces), each call checked."""
+    ctx = gpu_ctx
+    N = 30000
+    degrees = [20000, 0, 1, 33, 5000, 31, 0, 12000, 2, 700, 64, 65, 0, 300] * 3
+    rp, ci, v = random_csr(len(degrees), N, degrees, seed=51)
+    M, nnz = len(degrees), len(ci)
+    B = pkg.host_fill_uniform(N * K, 51, 1, -1.0, 1.0).reshape(N, K)
+    ref, abs_sum = oracle.spmm_f64(rp, ci, v, B)
+    d_rp, d_ci, d_v, d_B = ctx.upload(rp), ctx.upload(ci), ctx.upload(v), ctx.upload(B)
+    d_C = ctx.alloc((M, K), np.float32)
+    opts = pkg.Opts(algo=pkg.ALGO_BALANCED, chunk_nnz=chunk)
+    plan = ctx.plan_create(M, nnz, d_rp, K, opts, N=N, col_idx=d_ci)
+    first = None
+    for call in range(3):
+        ctx.fill(d_C, M * K, float(call))            # stale contents differ from call to call
+        ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_B, d_C, plan=plan, opts=opts)
+        ctx.stream_sync()
+        got = d_C.to_host()
+        check_against_f64(got, ref, abs_sum, "settled in kernel, call %d" % call)
+        if first is None:
+            first = got
+        assert np.array_equal(got, first)            # bit-reproducible from call to call
+    # the same plan at a narrower width takes the separate fix-up kernel and leaves the counters alone
+    B32 = np.ascontiguousarray(B[:, :32])
+    d_B32, d_C32 = ctx.upload(B32), ctx.alloc((M, 32), np.float32)
+    ctx.spmm_csr(M, N, 32, nnz, d_rp, d_ci, d_v, d_B32, d_C32, plan=plan, opts=opts)
+    r32, a32 = oracle.spmm_f64(rp, ci, v, B32)
+    check_against_f64(d_C32.to_host(), r32, a32, "same plan, K = 32")
+    ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_B, d_C, plan=plan, opts=opts)
+    assert np.array_equal(d_C.to_host(), first)
+    ctx.plan_destroy(plan)
+    for b in (d_rp, d_ci, d_v, d_B, d_C, d_B32, d_C32):
+        b.free()
