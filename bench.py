@@ -348,7 +348,7 @@ def main():
     Kd = max(ks)
     alg_bytes = pkg.spmm_algorithmic_bytes(M_l, n_ref, Kd, nnz_l)
     achieved = alg_bytes / (per_k_ms[Kd] * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "spmm_warp_kernel K=%d (+carry fix-up)" % Kd,
+    roofline = {"bound": "hbm", "kernel": "spmm_warp_kernel K=%d (carries of split rows settled inside it)" % Kd,
                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_K128 if (n_gpus == 1 and Kd == 128) else None,
                 "algorithmic_bytes": alg_bytes, "ms": per_k_ms[Kd],
