@@ -659,6 +659,125 @@ __device__ __forceinline__ void add_carries_grouped(const float* __restrict__ sr
   }
 }
 
+// Fix-up for K = 4*W in {32, 64, 128} when the nominal chunk size S is known.  A block takes
+// CB = 256 / W consecutive chunks, one group of W lanes per chunk, each lane owning four columns.
+// A row longer than S is cut at multiples of S only, so the carries of row r sit in chunks
+// first = row_ptr[r] / S .. last - 1 with last = (row_ptr[r+1] - 1) / S: the group of chunk `first`
+// needs two loads to know the whole run, where a scan of carry_row would take one round trip per
+// 32 chunks.  Short runs (a row of 300 entries has one or two carries) are summed by that group;
+// tens of thousands of such independent walks hide each other's latency.  A run longer than
+// kLongRun (a row of many thousand entries; at most one can start in a block, since it covers every
+// later chunk of the block) is summed by the whole block: group g takes carries g, g + CB, ..., and
+// the groups are combined pairwise in shared memory in a fixed order.
+// The order of additions depends only on the chunking, never on timing.
+constexpr int kLongRun = 32;
+
+template <int W>
+__global__ void __launch_bounds__(kBlockThreads)
+carry_fixup_grouped_kernel(int n_chunks, int S, const int* __restrict__ row_ptr,
+                           const int* __restrict__ carry_row, const float* __restrict__ carry_val,
+                           float* __restrict__ C) {
+  constexpr int K = 4 * W;
+  constexpr int CB = kBlockThreads / W;
+  __shared__ int long_head, long_len, long_row;
+  __shared__ float4 part[CB][W];
+  const int g = threadIdx.x / W, l = threadIdx.x % W;
+  const int64_t c = (int64_t)blockIdx.x * CB + g;
+  if (threadIdx.x == 0) long_len = 0;
+  __syncthreads();
+
+  const int row = c < n_chunks ? carry_row[c] : -1;
+  if (row >= 0) {
+    const int first = __ldg(row_ptr + row) / S;
+    if (c == first) {
+      const int len = (__ldg(row_ptr + row + 1) - 1) / S - first;
+      if (len > kLongRun) {
+        if (l == 0) {
+          long_head = g;
+          long_len = len;
+          long_row = row;
+        }
+      } else {
+        const float* src = carry_val + c * K + l * 4;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        int i = 0;
+        for (; i + 4 <= len; i += 4) {
+          float4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float4*>(src + (int64_t)(i + u) * K);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            s.x += v[u].x;
+            s.y += v[u].y;
+            s.z += v[u].z;
+            s.w += v[u].w;
+          }
+        }
+        for (; i < len; ++i) {
+          const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)i * K);
+          s.x += v.x;
+          s.y += v.y;
+          s.z += v.z;
+          s.w += v.w;
+        }
+        float4* out = reinterpret_cast<float4*>(C + (int64_t)row * K + l * 4);
+        float4 o = *out;
+        o.x += s.x;
+        o.y += s.y;
+        o.z += s.z;
+        o.w += s.w;
+        *out = o;
+      }
+    }
+  }
+  __syncthreads();
+  const int len = long_len;
+  if (len == 0) return;   // block-uniform
+
+  const float* src = carry_val + ((int64_t)blockIdx.x * CB + long_head) * K + l * 4;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  int i = g;
+  for (; i + 3 * CB < len; i += 4 * CB) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float4*>(src + (int64_t)(i + u * CB) * K);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s.x += v[u].x;
+      s.y += v[u].y;
+      s.z += v[u].z;
+      s.w += v[u].w;
+    }
+  }
+  for (; i < len; i += CB) {
+    const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)i * K);
+    s.x += v.x;
+    s.y += v.y;
+    s.z += v.z;
+    s.w += v.w;
+  }
+  part[g][l] = s;
+  __syncthreads();
+#pragma unroll
+  for (int o = CB / 2; o > 0; o >>= 1) {
+    if (g < o) {
+      const float4 a = part[g][l], b = part[g + o][l];
+      part[g][l] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+    }
+    __syncthreads();
+  }
+  if (g == 0) {
+    const float4 t = part[0][l];
+    float4* out = reinterpret_cast<float4*>(C + (int64_t)long_row * K + l * 4);
+    float4 o = *out;
+    o.x += t.x;
+    o.y += t.y;
+    o.z += t.z;
+    o.w += t.w;
+    *out = o;
+  }
+}
+
 __global__ void __launch_bounds__(kBlockThreads)
 carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
                    const float* __restrict__ carry_val, float* __restrict__ C) {
@@ -1106,7 +1225,15 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
   if (st != HPSPMM_OK) return st;
   if (!rowsplit && need_fixup && n_chunks > 0 && !in_kernel_fixup) {
     const unsigned blocks = (unsigned)((n_chunks + kBlockThreads - 1) / kBlockThreads);
-    carry_fixup_kernel<<<blocks, kBlockThreads, 0, stream>>>((int)K, nc, carry_row, carry_val, C);
+    const unsigned gblocks = (unsigned)((n_chunks * (K / 4) + kBlockThreads - 1) / kBlockThreads);
+    if (S > 0 && K == 32)
+      carry_fixup_grouped_kernel<8><<<gblocks, kBlockThreads, 0, stream>>>(nc, S, row_ptr, carry_row, carry_val, C);
+    else if (S > 0 && K == 64)
+      carry_fixup_grouped_kernel<16><<<gblocks, kBlockThreads, 0, stream>>>(nc, S, row_ptr, carry_row, carry_val, C);
+    else if (S > 0 && K == 128)
+      carry_fixup_grouped_kernel<32><<<gblocks, kBlockThreads, 0, stream>>>(nc, S, row_ptr, carry_row, carry_val, C);
+    else
+      carry_fixup_kernel<<<blocks, kBlockThreads, 0, stream>>>((int)K, nc, carry_row, carry_val, C);
     ctx->launches++;
     HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   }
@@ -1258,7 +1385,7 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
                                    sort_scratch, s);
   if (st != HPSPMM_OK) return st;
   return run_spmm(ctx, hint, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
-                  chunk_row, carry_row, carry_val, chunk_order, true, s);
+                  chunk_row, carry_row, carry_val, chunk_order, true, s, S);
 }
 
 // Host-buffer product, pipelined over 32-column slabs when K is a multiple of 32 and K >= 64:
@@ -1563,7 +1690,7 @@ extern "C" int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M,
                                  nullptr, s);
   if (st == HPSPMM_OK)
     st = run_spmm(&local, K >= 64, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
-                  chunk_row, carry_row, carry_val, /*chunk_order=*/nullptr, true, s);
+                  chunk_row, carry_row, carry_val, /*chunk_order=*/nullptr, true, s, S);
   if (st != HPSPMM_OK) write_err(err_buf, err_len, local.err);
   return st;
 }
