@@ -254,3 +254,32 @@ def test_split_rows_settled_inside_the_kernel_on_repeated_calls(gpu_ctx, pkg, or
     ctx.plan_destroy(plan)
     for b in (d_rp, d_ci, d_v, d_B, d_C, d_B32, d_C32):
         b.free()
+
+
+def _structured_degree_lists(S):
+    """Row-length patterns around the nominal chunk size S: rows that end or start exactly on a cut, rows one
+    longer or shorter than a chunk, heavy rows first, last, adjacent, and separated by empty rows."""
+    yield [S, S + 1, 2 * S, 2 * S - 1, 0, S - 1, 1, 3 * S + 5, 0, 0, S]
+    yield [S + 1]
+    yield [5 * S]
+    yield [1, 5 * S]
+    yield [S - 1, S + 1, S - 1, S + 1]
+    yield [3 * S, 3 * S, 3 * S]
+    yield [0, 0, 4 * S + 1, 0, 0, 7, 0]
+    yield [S // 2] * 9 + [2 * S + S // 2] + [S // 2] * 3
+    yield [1] * (2 * S) + [10 * S + 3] + [2] * S
+    yield [S - 1, 1, S, S, 1, S - 1, 2 * S, 1]
+    yield [40 * S + 17, 3, 33 * S, 0, 35 * S - 1]      # runs longer than 32 carries
+
+
+@pytest.mark.parametrize("K", [32, 64, 128, 24])
+@pytest.mark.parametrize("chunk", [32, 128])
+def test_rows_around_the_chunk_size(gpu_ctx, pkg, oracle, K, chunk):
+    N = 20000
+    for case, degrees in enumerate(_structured_degree_lists(chunk)):
+        rp, ci, v = random_csr(len(degrees), N, degrees, seed=60 + case)
+        B = pkg.host_fill_uniform(N * K, 60 + case, 1, -1.0, 1.0).reshape(N, K)
+        opts = pkg.Opts(algo=pkg.ALGO_BALANCED, chunk_nnz=chunk)
+        for use_plan in (False, True):
+            _check(gpu_ctx, pkg, oracle, rp, ci, v, B, "S=%d case %d plan=%s K=%d" % (chunk, case, use_plan, K),
+                   opts=opts, use_plan=use_plan)
