@@ -55,6 +55,42 @@ def test_coo_reordered_rows_and_nan_in_padding_row(gpu_ctx, pkg, oracle):
         b.free()
 
 
+@pytest.mark.parametrize("K", [32, 64, 128, 48])
+@pytest.mark.parametrize("order", ["shuffled", "heavy_rows", "padded_inside"])
+def test_coo_triples_in_any_order(gpu_ctx, pkg, oracle, K, order):
+    """The COO contract puts no order on the triples: entries of one row scattered over many chunks, runs of
+    thousands of equal row ids, and zero-valued padding in the middle of the array all give A·B."""
+    ctx = gpu_ctx
+    rng = np.random.default_rng(17)
+    if order == "heavy_rows":
+        rp, ci, v = random_csr(12, 9000, [6000, 0, 1, 33, 2500, 31, 0, 4000, 2, 700, 64, 65], seed=18)
+        M, N = 12, 9000
+    else:
+        g = pkg.gen_rmat(11, 16, seed=19)
+        rp, ci, v, M, N = g["row_ptr"], g["col_idx"], g["vals"], g["M"], g["N"]
+    v = np.where(v == 0, np.float32(0.5), v).astype(np.float32)     # keep stored entries distinguishable from padding
+    r = np.repeat(np.arange(M, dtype=np.int32), np.diff(rp))
+    c = ci.copy()
+    w = v.copy()
+    if order == "shuffled":
+        p = rng.permutation(len(r))
+        r, c, w = r[p], c[p], w[p]
+    elif order == "padded_inside":
+        pos = np.sort(rng.choice(len(r) + 1, size=200, replace=True))
+        r = np.insert(r, pos, 0).astype(np.int32)
+        c = np.insert(c, pos, 0).astype(np.int32)
+        w = np.insert(w, pos, np.float32(0)).astype(np.float32)
+    B = pkg.host_fill_uniform(N * K, 17, K, -1.0, 1.0).reshape(N, K)
+    ref, abs_sum = oracle.spmm_f64(rp, ci, v, B)
+    d_r, d_c, d_w, d_B = ctx.upload(r), ctx.upload(c), ctx.upload(w), ctx.upload(B)
+    buf, c_ptr, read = guarded_output(ctx, (M, K), fill=np.float32(0))
+    ctx.spmm_coo(M, N, K, len(r), d_r, d_c, d_w, d_B, c_ptr)
+    ctx.stream_sync()
+    check_against_f64(read(), ref, abs_sum, "coo %s K=%d" % (order, K))
+    for b in (d_r, d_c, d_w, d_B, buf):
+        b.free()
+
+
 @pytest.mark.parametrize("K", [32, 64, 128, 4, 20, 33, 200, 1])
 @pytest.mark.parametrize("use_plan", [False, True])
 def test_sddmm(gpu_ctx, pkg, oracle, K, use_plan):
