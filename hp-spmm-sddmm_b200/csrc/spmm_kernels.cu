@@ -617,48 +617,6 @@ spmm_generic_kernel(int M, int K, int n_chunks, int n_chunk_blocks, const int* _
 }
 
 // ---- carries ---------------------------------------------------------------------------
-// One lane per chunk finds the first carry of each split row; the warp then counts that
-// row's carries (32 at a time) and sums them.  For K = 4*W <= 128 the warp works as
-// G = 32/W lane groups: group g sums carries g, g+G, ... four at a time with independent
-// loads, the groups are combined in a fixed order, and the total is added to the row its
-// owner stored.  The order of additions depends only on the chunking, never on timing.
-template <int W>
-__device__ __forceinline__ void add_carries_grouped(const float* __restrict__ src, int64_t len, int K,
-                                                    float* __restrict__ crow, int lane) {
-  constexpr int G = 32 / W;
-  const int g = lane / W, l = lane % W;
-  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-  int64_t i = g;
-  for (; i + 3 * G < len; i += 4 * G) {
-    float4 t[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) t[u] = *reinterpret_cast<const float4*>(src + (i + u * G) * K + l * 4);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      s.x += t[u].x;
-      s.y += t[u].y;
-      s.z += t[u].z;
-      s.w += t[u].w;
-    }
-  }
-  for (; i < len; i += G) {
-    const float4 t = *reinterpret_cast<const float4*>(src + i * K + l * 4);
-    s.x += t.x;
-    s.y += t.y;
-    s.z += t.z;
-    s.w += t.w;
-  }
-  s = reduce_groups<W>(s);
-  if (g == 0) {
-    float4 o = *reinterpret_cast<float4*>(crow + l * 4);
-    o.x += s.x;
-    o.y += s.y;
-    o.z += s.z;
-    o.w += s.w;
-    *reinterpret_cast<float4*>(crow + l * 4) = o;
-  }
-}
-
 // Fix-up for K = 4*W in {32, 64, 128} when the nominal chunk size S is known.  A block takes
 // CB = 256 / W consecutive chunks, one group of W lanes per chunk, each lane owning four columns.
 // A row longer than S is cut at multiples of S only, so the carries of row r sit in chunks
@@ -778,6 +736,8 @@ carry_fixup_grouped_kernel(int n_chunks, int S, const int* __restrict__ row_ptr,
   }
 }
 
+// Fix-up for any other K: one lane per chunk finds the first carry of each split row; the warp then
+// counts that row's carries (32 at a time) and sums them in chunk order, lanes owning columns.
 __global__ void __launch_bounds__(kBlockThreads)
 carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
                    const float* __restrict__ carry_val, float* __restrict__ C) {
@@ -809,13 +769,7 @@ carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
     }
     float* crow = C + (int64_t)hr * K;
     const float* src = carry_val + first * K;
-    if (K == 32) {
-      add_carries_grouped<8>(src, len, K, crow, lane);
-    } else if (K == 64) {
-      add_carries_grouped<16>(src, len, K, crow, lane);
-    } else if (K == 128) {
-      add_carries_grouped<32>(src, len, K, crow, lane);
-    } else if ((K & 3) == 0) {
+    if ((K & 3) == 0) {
       for (int col = lane * 4; col < K; col += 128) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int64_t i = 0; i < len; ++i) {
