@@ -22,8 +22,10 @@ struct hpspmm_layer {
   int32_t* col_idx_t;
   float* vals_t;
   int32_t* perm;
-  hpspmm_plan* plan;
-  hpspmm_plan* plan_t;
+  // chunk tables per width class (K <= 32, <= 64, wider): the best chunk size depends on K.
+  // The class of max_K is built by create, the others on first use.
+  hpspmm_plan* plan[3];
+  hpspmm_plan* plan_t[3];
   size_t bytes;
 };
 
@@ -40,13 +42,33 @@ __global__ void gather_by_perm_kernel(int64_t n, const int* __restrict__ perm, c
 
 void release(hpspmm_ctx* ctx, hpspmm_layer* g) {
   if (!g) return;
-  if (g->plan) hpspmm_plan_destroy(ctx, g->plan);
-  if (g->plan_t) hpspmm_plan_destroy(ctx, g->plan_t);
+  for (int i = 0; i < 3; ++i) {
+    if (g->plan[i]) hpspmm_plan_destroy(ctx, g->plan[i]);
+    if (g->plan_t[i]) hpspmm_plan_destroy(ctx, g->plan_t[i]);
+  }
   cudaFree(g->row_ptr_t);
   cudaFree(g->col_idx_t);
   cudaFree(g->vals_t);
   cudaFree(g->perm);
   delete g;
+}
+
+int width_class(int64_t K) { return K <= 32 ? 0 : (K <= 64 ? 1 : 2); }
+
+// plans of A and of its transpose for the width class of K, built on first use
+int plans_for(hpspmm_ctx* ctx, hpspmm_layer* g, int64_t K, hpspmm_stream stream, int* cls_out) {
+  const int cls = width_class(K);
+  *cls_out = cls;
+  if (g->plan[cls] && g->plan_t[cls]) return HPSPMM_OK;
+  const int64_t width = cls == 0 ? 32 : (cls == 1 ? 64 : g->max_K);
+  int st = HPSPMM_OK;
+  if (!g->plan[cls])
+    st = hpspmm_plan_create(ctx, g->M, g->N, g->nnz, g->row_ptr, g->col_idx, width, nullptr, stream, &g->plan[cls]);
+  if (st == HPSPMM_OK && !g->plan_t[cls])
+    st = hpspmm_plan_create(ctx, g->N, g->M, g->nnz, g->row_ptr_t, g->col_idx_t, width, nullptr, stream,
+                            &g->plan_t[cls]);
+  if (st == HPSPMM_OK) g->bytes += g->plan[cls]->bytes + g->plan_t[cls]->bytes;
+  return st;
 }
 
 }  // namespace
@@ -86,15 +108,12 @@ int hpspmm_layer_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, cons
   g->bytes = b_rp + 3 * b_e;
   int st = hpspmm_csr_transpose(ctx, M, N, nnz, row_ptr, col_idx, vals, g->row_ptr_t, g->col_idx_t,
                                 vals ? g->vals_t : nullptr, g->perm, stream);
-  if (st == HPSPMM_OK)
-    st = hpspmm_plan_create(ctx, M, N, nnz, row_ptr, col_idx, max_K, nullptr, stream, &g->plan);
-  if (st == HPSPMM_OK)
-    st = hpspmm_plan_create(ctx, N, M, nnz, g->row_ptr_t, g->col_idx_t, max_K, nullptr, stream, &g->plan_t);
+  int cls = 0;
+  if (st == HPSPMM_OK) st = plans_for(ctx, g, max_K, stream, &cls);
   if (st != HPSPMM_OK) {
     release(ctx, g);
     return st;
   }
-  g->bytes += g->plan->bytes + g->plan_t->bytes;
   *out = g;
   return HPSPMM_OK;
 }
@@ -128,27 +147,36 @@ int hpspmm_layer_transposed(const hpspmm_layer* g, const int32_t** row_ptr_t, co
   return HPSPMM_OK;
 }
 
-int hpspmm_layer_forward(hpspmm_ctx* ctx, const hpspmm_layer* g, int64_t K, const float* H, float* C,
+int hpspmm_layer_forward(hpspmm_ctx* ctx, hpspmm_layer* g, int64_t K, const float* H, float* C,
                          hpspmm_stream stream) {
   HPSPMM_REQUIRE(ctx, ctx != nullptr && g != nullptr, "null context or layer");
   HPSPMM_REQUIRE(ctx, K >= 1 && K <= g->max_K, "K outside [1, max_K] of the layer");
-  return hpspmm_spmm_csr_f32(ctx, g->plan, g->M, g->N, K, g->nnz, g->row_ptr, g->col_idx, g->vals, H, C,
+  int cls;
+  const int st = plans_for(ctx, g, K, stream, &cls);
+  if (st != HPSPMM_OK) return st;
+  return hpspmm_spmm_csr_f32(ctx, g->plan[cls], g->M, g->N, K, g->nnz, g->row_ptr, g->col_idx, g->vals, H, C,
                              nullptr, stream);
 }
 
-int hpspmm_layer_backward_features(hpspmm_ctx* ctx, const hpspmm_layer* g, int64_t K, const float* dC,
+int hpspmm_layer_backward_features(hpspmm_ctx* ctx, hpspmm_layer* g, int64_t K, const float* dC,
                                    float* dH, hpspmm_stream stream) {
   HPSPMM_REQUIRE(ctx, ctx != nullptr && g != nullptr, "null context or layer");
   HPSPMM_REQUIRE(ctx, K >= 1 && K <= g->max_K, "K outside [1, max_K] of the layer");
-  return hpspmm_spmm_csr_f32(ctx, g->plan_t, g->N, g->M, K, g->nnz, g->row_ptr_t, g->col_idx_t, g->vals_t, dC,
+  int cls;
+  const int st = plans_for(ctx, g, K, stream, &cls);
+  if (st != HPSPMM_OK) return st;
+  return hpspmm_spmm_csr_f32(ctx, g->plan_t[cls], g->N, g->M, K, g->nnz, g->row_ptr_t, g->col_idx_t, g->vals_t, dC,
                              dH, nullptr, stream);
 }
 
-int hpspmm_layer_backward_weights(hpspmm_ctx* ctx, const hpspmm_layer* g, int64_t K, const float* dC,
+int hpspmm_layer_backward_weights(hpspmm_ctx* ctx, hpspmm_layer* g, int64_t K, const float* dC,
                                   const float* H, float* dA, hpspmm_stream stream) {
   HPSPMM_REQUIRE(ctx, ctx != nullptr && g != nullptr, "null context or layer");
   HPSPMM_REQUIRE(ctx, K >= 1 && K <= g->max_K, "K outside [1, max_K] of the layer");
-  return hpspmm_sddmm_csr_f32(ctx, g->plan, g->M, g->N, K, g->nnz, g->row_ptr, g->col_idx, dC, H, dA, nullptr,
+  int cls;
+  const int st = plans_for(ctx, g, K, stream, &cls);
+  if (st != HPSPMM_OK) return st;
+  return hpspmm_sddmm_csr_f32(ctx, g->plan[cls], g->M, g->N, K, g->nnz, g->row_ptr, g->col_idx, dC, H, dA, nullptr,
                               stream);
 }
 

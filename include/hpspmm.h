@@ -240,8 +240,10 @@ HPSPMM_API int hpspmm_csr_transpose(hpspmm_ctx* ctx, int64_t M, int64_t N, int64
  *   backward_features  dH = A^T * dC      dC is M x K, dH is N x K
  *   backward_weights   dA[j] = dot(dC[row(j),:], H[col[j],:])   (nnz values, CSR order)
  *   update_values      new vals pointer; the transpose's values are re-gathered from it
- * create synchronises the stream (it builds two plans); the other calls only enqueue.
- * Calls on one handle must not overlap on the GPU. */
+ * The best chunk size depends on K, so the handle keeps one pair of plans per width class
+ * (K <= 32, K <= 64, wider).  create builds the pair for max_K and synchronises the stream;
+ * the first product at a width of another class builds that pair (synchronising once more);
+ * every other call only enqueues.  Calls on one handle must not overlap on the GPU. */
 typedef struct hpspmm_layer hpspmm_layer;
 HPSPMM_API int hpspmm_layer_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz,
                                    const int32_t* row_ptr, const int32_t* col_idx,
@@ -254,12 +256,12 @@ HPSPMM_API int hpspmm_layer_info(const hpspmm_layer* layer, int64_t* M, int64_t*
 HPSPMM_API int hpspmm_layer_transposed(const hpspmm_layer* layer, const int32_t** row_ptr_t,
                                        const int32_t** col_idx_t, const float** vals_t,
                                        const int32_t** perm);
-HPSPMM_API int hpspmm_layer_forward(hpspmm_ctx* ctx, const hpspmm_layer* layer, int64_t K,
+HPSPMM_API int hpspmm_layer_forward(hpspmm_ctx* ctx, hpspmm_layer* layer, int64_t K,
                                     const float* H, float* C, hpspmm_stream stream);
-HPSPMM_API int hpspmm_layer_backward_features(hpspmm_ctx* ctx, const hpspmm_layer* layer,
+HPSPMM_API int hpspmm_layer_backward_features(hpspmm_ctx* ctx, hpspmm_layer* layer,
                                               int64_t K, const float* dC, float* dH,
                                               hpspmm_stream stream);
-HPSPMM_API int hpspmm_layer_backward_weights(hpspmm_ctx* ctx, const hpspmm_layer* layer,
+HPSPMM_API int hpspmm_layer_backward_weights(hpspmm_ctx* ctx, hpspmm_layer* layer,
                                              int64_t K, const float* dC, const float* H,
                                              float* dA, hpspmm_stream stream);
 HPSPMM_API int hpspmm_layer_update_values(hpspmm_ctx* ctx, hpspmm_layer* layer,
