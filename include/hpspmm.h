@@ -126,6 +126,8 @@ HPSPMM_API int hpspmm_host_fill_uniform_f32(float* host_ptr, int64_t count, uint
  * plan may be NULL: the chunk table is then rebuilt into context-owned scratch on
  * every call (one extra small kernel).  The first call that needs more scratch than
  * the context holds allocates it (cudaMalloc, synchronising); later calls do not.
+ * With a plan the call only enqueues kernels (no allocation, no synchronisation), so it can
+ * be recorded into a CUDA graph and replayed.
  * Calls that share a context or a plan must not overlap on the GPU. */
 HPSPMM_API int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M,
                                    int64_t N, int64_t K, int64_t nnz, const int32_t* row_ptr,

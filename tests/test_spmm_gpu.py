@@ -283,3 +283,49 @@ def test_rows_around_the_chunk_size(gpu_ctx, pkg, oracle, K, chunk):
         for use_plan in (False, True):
             _check(gpu_ctx, pkg, oracle, rp, ci, v, B, "S=%d case %d plan=%s K=%d" % (chunk, case, use_plan, K),
                    opts=opts, use_plan=use_plan)
+
+
+def test_products_with_a_plan_can_be_captured_in_a_cuda_graph(pkg, oracle):
+    """With a plan a product only enqueues kernels (no allocation, no synchronisation), so a training step's
+    products can be recorded once into a CUDA graph and replayed; the carry counters return to zero by themselves."""
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda", 0)
+    ctx = pkg.Context(0)
+    g = pkg.gen_rmat(13, 16, seed=71)
+    M, N, nnz = g["M"], g["N"], g["nnz"]
+    rp, ci, v = (torch.from_numpy(g[k]).to(dev) for k in ("row_ptr", "col_idx", "vals"))
+    Ks = (32, 64, 128)
+    Bh = {K: pkg.host_fill_uniform(N * K, 71, K, -1.0, 1.0).reshape(N, K) for K in Ks}
+    B = {K: torch.from_numpy(Bh[K]).to(dev) for K in Ks}
+    C = {K: torch.full((M, K), 7.0, dtype=torch.float32, device=dev) for K in Ks}
+    plans = {K: ctx.plan_create(M, nnz, rp.data_ptr(), K, N=N, col_idx=ci.data_ptr()) for K in Ks}
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        for K in Ks:   # warm-up outside the capture
+            ctx.spmm_csr(M, N, K, nnz, rp.data_ptr(), ci.data_ptr(), v.data_ptr(), B[K].data_ptr(), C[K].data_ptr(),
+                         plan=plans[K], stream=side.cuda_stream)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            s = torch.cuda.current_stream(dev).cuda_stream
+            for K in Ks:
+                ctx.spmm_csr(M, N, K, nnz, rp.data_ptr(), ci.data_ptr(), v.data_ptr(), B[K].data_ptr(),
+                             C[K].data_ptr(), plan=plans[K], stream=s)
+    first = None
+    for replay in range(3):
+        for K in Ks:
+            C[K].fill_(float(replay))
+        graph.replay()
+        torch.cuda.synchronize(dev)
+        got = {K: C[K].cpu().numpy() for K in Ks}
+        for K in Ks:
+            ref, abs_sum = oracle.spmm_f64(g["row_ptr"], g["col_idx"], g["vals"], Bh[K])
+            check_against_f64(got[K], ref, abs_sum, "graph replay %d K=%d" % (replay, K))
+        if first is None:
+            first = got
+        assert all(np.array_equal(got[K], first[K]) for K in Ks)
+    del graph
+    for K in Ks:
+        ctx.plan_destroy(plans[K])
+    ctx.close()
