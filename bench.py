@@ -385,7 +385,10 @@ def main():
         compare = {"cusparse_csr_ms": {}, "note": "torch.sparse CSR @ dense (cuSPARSE SpMM), same operands, "
                    "3 warm-up + 10 timed launches, CUDA events"}
         try:
-            A_t = torch.sparse_csr_tensor(t_rp.to(torch.int64), t_ci.to(torch.int64), t_v, size=(M_l, N))
+            import warnings
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")   # torch announces that sparse CSR support is in beta
+                A_t = torch.sparse_csr_tensor(t_rp.to(torch.int64), t_ci.to(torch.int64), t_v, size=(M_l, N))
             for K in ks:
                 for _ in range(3):
                     out = A_t @ Bs[K]
