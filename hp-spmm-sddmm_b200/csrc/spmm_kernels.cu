@@ -65,7 +65,9 @@ __global__ void chunk_table_kernel(int M, int nnz, const int* __restrict__ row_p
 // Blocks past the chunk blocks walk all rows and write zeros into the empty ones.
 __device__ __forceinline__ void zero_empty_rows(int M, int K, const int* __restrict__ row_ptr,
                                                 float* __restrict__ C, int zero_block,
-                                                int n_zero_blocks, int block_threads = kBlockThreads) {
+                                                int n_zero_blocks, int block_threads = kBlockThreads,
+                                                int64_t row_stride = 0) {
+  if (row_stride == 0) row_stride = K;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int warps_per_block = block_threads / 32;
@@ -78,7 +80,7 @@ __device__ __forceinline__ void zero_empty_rows(int M, int K, const int* __restr
     while (m) {
       const int b = __ffs(m) - 1;
       m &= m - 1;
-      float* crow = C + (r0 + b) * (int64_t)K;
+      float* crow = C + (r0 + b) * row_stride;
       if ((K & 3) == 0) {
         for (int c = lane * 4; c < K; c += 128) st_stream(crow + c, make_float4(0.f, 0.f, 0.f, 0.f));
       } else {
@@ -289,8 +291,8 @@ __device__ __forceinline__ float4 reduce_groups(float4 a) {
 template <int W>
 __device__ __noinline__ void settle_split_row(int r, int r_end, int S, const int* __restrict__ row_ptr,
                                               const float* __restrict__ carry_val, float* __restrict__ C,
-                                              int* __restrict__ run_counter) {
-  constexpr int K = 4 * W;
+                                              int* __restrict__ run_counter, int ld) {
+  const int64_t K = ld;   // row stride of C and of the carry slots (the slab is 4 * W columns wide)
   constexpr int G = 32 / W;
   const int lane = threadIdx.x & 31;
   const int g = lane / W, l = lane % W;
@@ -337,15 +339,18 @@ __device__ __noinline__ void settle_split_row(int r, int r_end, int S, const int
   if (lane == 0) run_counter[first] = 0;   // ready for the next launch
 }
 
-template <int W, int U, int MINB, bool HINT, int BT, bool SETTLE>
+template <int W, int U, int MINB, bool HINT, int BT, bool SETTLE, bool STRIDED>
 __global__ void __launch_bounds__(BT, MINB)
 spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict__ row_ptr,
                  const int* __restrict__ col_idx, const float* __restrict__ vals,
                  const float* __restrict__ B, float* __restrict__ C,
                  const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
                  int* __restrict__ carry_row, float* __restrict__ carry_val,
-                 const int* __restrict__ chunk_order, int S, int* __restrict__ run_counter) {
-  constexpr int K = 4 * W;
+                 const int* __restrict__ chunk_order, int S, int* __restrict__ run_counter, int ld) {
+  // The kernel computes a slab of KW = 4 * W columns.  STRIDED: the slab is part of wider matrices, B, C
+  // and the carry slots have row stride ld; otherwise the stride is the compile-time KW.
+  constexpr int KW = 4 * W;
+  const int64_t K = STRIDED ? (int64_t)ld : (int64_t)KW;
   constexpr int G = 32 / W;      // lane groups = entries gathered per warp instruction
   constexpr int T = 32;          // entries per staged tile
   constexpr int BATCH = U * G;   // entries per batch of gathers
@@ -354,7 +359,7 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   __shared__ int2 tiles[BT / 32][STAGES][T];
 
   if ((int)blockIdx.x >= n_chunk_blocks) {
-    zero_empty_rows(M, K, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks, BT);
+    zero_empty_rows(M, KW, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks, BT, K);
     return;
   }
   const int lane = threadIdx.x & 31;
@@ -496,8 +501,8 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   if (!hands_on && !stores_split_row) return;
   __threadfence();
   __syncwarp();   // every lane's part is visible before lane 0 bumps a counter
-  if (stores_split_row) settle_split_row<W>(r0, r0_end, S, row_ptr, carry_val, C, run_counter);
-  if (hands_on) settle_split_row<W>(row, row_end, S, row_ptr, carry_val, C, run_counter);
+  if (stores_split_row) settle_split_row<W>(r0, r0_end, S, row_ptr, carry_val, C, run_counter, (int)K);
+  if (hands_on) settle_split_row<W>(row, row_end, S, row_ptr, carry_val, C, run_counter, (int)K);
 }
 
 // ---- generic kernel: any K -------------------------------------------------------------
@@ -634,8 +639,8 @@ template <int W>
 __global__ void __launch_bounds__(kBlockThreads)
 carry_fixup_grouped_kernel(int n_chunks, int S, const int* __restrict__ row_ptr,
                            const int* __restrict__ carry_row, const float* __restrict__ carry_val,
-                           float* __restrict__ C) {
-  constexpr int K = 4 * W;
+                           float* __restrict__ C, int ld) {
+  const int64_t K = ld;   // row stride of C and of the carry slots; the slab is 4 * W columns wide
   constexpr int CB = kBlockThreads / W;
   __shared__ int long_head, long_len, long_row;
   __shared__ float4 part[CB][W];
@@ -1039,11 +1044,12 @@ int launch_balanced(hpspmm_ctx* ctx, bool hint, bool rowsplit, int M, int n_chun
   return HPSPMM_OK;
 }
 
-template <int W, int U, int MINB, int BT = kBlockThreads>
+template <int W, int U, int MINB, int BT = kBlockThreads, bool STRIDED = false>
 int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* row_ptr,
                 const int32_t* col_idx, const float* vals, const float* B, float* C,
                 const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
-                float* carry_val, const int32_t* chunk_order, int S, int* run_counter, cudaStream_t stream) {
+                float* carry_val, const int32_t* chunk_order, int S, int* run_counter, cudaStream_t stream,
+                int ld = 4 * W) {
   const int chunks_per_block = BT / 32;
   const int n_chunk_blocks = (n_chunks + chunks_per_block - 1) / chunks_per_block;
   int n_zero_blocks = (M + BT - 1) / BT;
@@ -1052,9 +1058,9 @@ int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* 
   const unsigned grid = (unsigned)(n_chunk_blocks + n_zero_blocks);
   if (grid == 0) return HPSPMM_OK;
 #define HPSPMM_LAUNCH_WARP(H, ST)                                                               \
-  spmm_warp_kernel<W, U, MINB, H, BT, ST><<<grid, BT, 0, stream>>>(                                \
+  spmm_warp_kernel<W, U, MINB, H, BT, ST, STRIDED><<<grid, BT, 0, stream>>>(                       \
       M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, \
-      carry_val, chunk_order, S, run_counter)
+      carry_val, chunk_order, S, run_counter, ld)
   if (run_counter != nullptr) {
     if (hint) HPSPMM_LAUNCH_WARP(true, true); else HPSPMM_LAUNCH_WARP(false, true);
   } else {
@@ -1144,6 +1150,43 @@ int check_spmm_args(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nn
   return HPSPMM_OK;
 }
 
+// One slab of 4 * W columns with the warp kernel, then its carries.  STRIDED: the slab is part of wider
+// matrices (B, C and the carry slots have row stride ld, the pointers already point at the slab's first
+// column).  With a counter array, slabs of 64 or 128 columns add the carries themselves.  Measured on the
+// R-MAT bench graph against the separate fix-up launch: -6 % at 128 columns, -2 % at 64, but +7 % at 32,
+// where chunks are short and the device-wide fence every piece of a split row takes weighs more than the
+// launch saved.
+// Tuning on B200 (R-MAT scale 20): 64-thread blocks, U = 4 gather steps in flight per lane and at most
+// 51 registers (20 blocks per SM) beat 128/256-thread blocks, U = 2/8/16 and the 32/40/64/80-register
+// builds at every width.
+template <int W, bool STRIDED>
+int run_slab(hpspmm_ctx* ctx, bool hint, int m, int nc, const int32_t* row_ptr, const int32_t* col_idx,
+             const float* vals, const float* B, float* C, const int32_t* chunk_start,
+             const int32_t* chunk_row, int32_t* carry_row, float* carry_val, const int32_t* chunk_order,
+             bool need_fixup, cudaStream_t stream, int S, int* run_counter, int ld) {
+  const bool settle = run_counter != nullptr && W >= 16;
+  // strided slabs carry two more live values (the stride) and spill at 48 registers: 16 blocks per SM
+  // (64 registers) took the K = 256 product from 1.44 to 1.20 ms
+  constexpr int MINB = STRIDED ? 16 : 20;
+  int st = launch_warp<W, 4, MINB, 64, STRIDED>(ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start,
+                                                chunk_row, carry_row, carry_val, chunk_order, S,
+                                                settle ? run_counter : nullptr, stream, ld);
+  if (st != HPSPMM_OK) return st;
+  if (need_fixup && nc > 0 && !settle) {
+    if (S > 0) {
+      const unsigned gblocks = (unsigned)(((int64_t)nc * W + kBlockThreads - 1) / kBlockThreads);
+      carry_fixup_grouped_kernel<W><<<gblocks, kBlockThreads, 0, stream>>>(nc, S, row_ptr, carry_row, carry_val,
+                                                                         C, ld);
+    } else {
+      const unsigned blocks = (unsigned)((nc + kBlockThreads - 1) / kBlockThreads);
+      carry_fixup_kernel<<<blocks, kBlockThreads, 0, stream>>>(4 * W, nc, carry_row, carry_val, C);
+    }
+    ctx->launches++;
+    HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  }
+  return HPSPMM_OK;
+}
+
 int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, int64_t n_chunks,
              const int32_t* row_ptr, const int32_t* col_idx, const float* vals, const float* B,
              float* C, const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
@@ -1151,43 +1194,52 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
              int S = 0, int* run_counter = nullptr) {
   int st;
   const int m = (int)M, nc = (int)n_chunks;
-  // With a counter array the warp kernels add the carries themselves.  Measured on the R-MAT bench graph
-  // against the separate fix-up kernel: -6 % at K = 128, -2 % at K = 64, but +7 % at K = 32, where chunks
-  // are short and the device-wide fence every piece of a split row takes weighs more than the launch saved.
-  const bool in_kernel_fixup = !rowsplit && run_counter != nullptr && (K == 64 || K == 128);
-  if (!in_kernel_fixup) run_counter = nullptr;
-  // Tuning on B200 (R-MAT scale 20): 64-thread blocks, U = 4 gather steps in flight per lane and
-  // at most 51 registers (20 blocks per SM) beat 128/256-thread blocks, U = 2/8/16 and the
-  // 32/40/64/80-register builds at every K.
 #define HPSPMM_ARGS ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, stream
-#define HPSPMM_WARGS ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, chunk_order, S, run_counter, stream
-  if (K == 32) {
-    st = rowsplit ? launch_balanced<8, 1, 8, 4>(HPSPMM_ARGS) : launch_warp<8, 4, 20, 64>(HPSPMM_WARGS);
-  } else if (K == 64) {
-    st = rowsplit ? launch_balanced<16, 1, 8, 4>(HPSPMM_ARGS) : launch_warp<16, 4, 20, 64>(HPSPMM_WARGS);
-  } else if (K == 128) {
-    st = rowsplit ? launch_balanced<32, 1, 8, 4>(HPSPMM_ARGS) : launch_warp<32, 4, 20, 64>(HPSPMM_WARGS);
+#define HPSPMM_SLAB(W, STRIDED, off) \
+  run_slab<W, STRIDED>(ctx, hint, m, nc, row_ptr, col_idx, vals, B + (off), C + (off), chunk_start, chunk_row, \
+                       carry_row, carry_val + (off), chunk_order, need_fixup, stream, S, run_counter, (int)K)
+  if (rowsplit && (K == 32 || K == 64 || K == 128)) {
+    st = K == 32 ? launch_balanced<8, 1, 8, 4>(HPSPMM_ARGS)
+                 : (K == 64 ? launch_balanced<16, 1, 8, 4>(HPSPMM_ARGS) : launch_balanced<32, 1, 8, 4>(HPSPMM_ARGS));
+    return st;
+  }
+  if (!rowsplit && K == 32) return HPSPMM_SLAB(8, false, 0);
+  if (!rowsplit && K == 64) return HPSPMM_SLAB(16, false, 0);
+  if (!rowsplit && K == 128) return HPSPMM_SLAB(32, false, 0);
+  if (!rowsplit && K % 32 == 0 && S > 0 && K <= 512) {
+    // any other multiple of 32 up to 512: column slabs of 128, then 64 and/or 32, each a strided run of the
+    // warp kernel (the sparse stream is read once per slab, as the reference's K / 32 grid rows read it).
+    // Measured on the R-MAT bench graph against the generic kernel: K = 96 0.73 vs 1.33 ms, 160 0.95 vs 1.49,
+    // 256 1.20 vs 1.61, 512 2.42 vs 2.51; beyond that the generic kernel's 2 KB contiguous gathers win.
+    int64_t off = 0;
+    while (K - off >= 128) {
+      st = HPSPMM_SLAB(32, true, off);
+      if (st != HPSPMM_OK) return st;
+      off += 128;
+    }
+    if (K - off >= 64) {
+      st = HPSPMM_SLAB(16, true, off);
+      if (st != HPSPMM_OK) return st;
+      off += 64;
+    }
+    if (K - off >= 32) {
+      st = HPSPMM_SLAB(8, true, off);
+      if (st != HPSPMM_OK) return st;
+    }
+    return HPSPMM_OK;
   }
 #undef HPSPMM_ARGS
-#undef HPSPMM_WARGS
-  else if ((K & 3) == 0)
+#undef HPSPMM_SLAB
+  if ((K & 3) == 0)
     st = launch_generic<4>(ctx, rowsplit, m, (int)K, nc, row_ptr, col_idx, vals, B, C, chunk_start,
                            chunk_row, carry_row, carry_val, chunk_order, stream);
   else
     st = launch_generic<1>(ctx, rowsplit, m, (int)K, nc, row_ptr, col_idx, vals, B, C, chunk_start,
                            chunk_row, carry_row, carry_val, chunk_order, stream);
   if (st != HPSPMM_OK) return st;
-  if (!rowsplit && need_fixup && n_chunks > 0 && !in_kernel_fixup) {
+  if (!rowsplit && need_fixup && n_chunks > 0) {
     const unsigned blocks = (unsigned)((n_chunks + kBlockThreads - 1) / kBlockThreads);
-    const unsigned gblocks = (unsigned)((n_chunks * (K / 4) + kBlockThreads - 1) / kBlockThreads);
-    if (S > 0 && K == 32)
-      carry_fixup_grouped_kernel<8><<<gblocks, kBlockThreads, 0, stream>>>(nc, S, row_ptr, carry_row, carry_val, C);
-    else if (S > 0 && K == 64)
-      carry_fixup_grouped_kernel<16><<<gblocks, kBlockThreads, 0, stream>>>(nc, S, row_ptr, carry_row, carry_val, C);
-    else if (S > 0 && K == 128)
-      carry_fixup_grouped_kernel<32><<<gblocks, kBlockThreads, 0, stream>>>(nc, S, row_ptr, carry_row, carry_val, C);
-    else
-      carry_fixup_kernel<<<blocks, kBlockThreads, 0, stream>>>((int)K, nc, carry_row, carry_val, C);
+    carry_fixup_kernel<<<blocks, kBlockThreads, 0, stream>>>((int)K, nc, carry_row, carry_val, C);
     ctx->launches++;
     HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   }

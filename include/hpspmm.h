@@ -121,7 +121,8 @@ HPSPMM_API int hpspmm_host_fill_uniform_f32(float* host_ptr, int64_t count, uint
  * the kernels it dispatches to (:247-387).  Argument order follows the reference's
  * kernels: (m, k, row_ptr, col_idx, values, B, C), with N and nnz added.  Overwrites C;
  * empty rows become zeros.  All pointers are device pointers.  K >= 1; K = 32/64/128
- * take the specialised kernels, other K a generic one.
+ * take the specialised kernels, every other multiple of 32 up to 512 runs them over
+ * column slabs of 128, 64 and 32, any other K a generic kernel.
  *
  * plan may be NULL: the chunk table is then rebuilt into context-owned scratch on
  * every call (one extra small kernel).  The first call that needs more scratch than
