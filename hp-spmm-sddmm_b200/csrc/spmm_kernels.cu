@@ -810,11 +810,12 @@ carry_fixup_kernel(int K, int n_chunks, const int* __restrict__ carry_row,
 // that lie inside one row.  Row boundaries come from the staged row ids (one ballot per tile)
 // instead of row_ptr; every run of equal row ids ends in one cross-group reduction and one
 // 16-byte vector reduction per lane of group 0 into C.
-template <int W, int U, int BT>
+template <int W, int U, int BT, bool STRIDED>
 __global__ void __launch_bounds__(BT, 16)
 spmm_coo_warp_kernel(int64_t nnz, int S, const int* __restrict__ row_idx, const int* __restrict__ col_idx,
-                     const float* __restrict__ vals, const float* __restrict__ B, float* __restrict__ C) {
-  constexpr int K = 4 * W;
+                     const float* __restrict__ vals, const float* __restrict__ B, float* __restrict__ C, int ld) {
+  // a slab of 4 * W columns; STRIDED: part of wider B and C with row stride ld
+  const int64_t K = STRIDED ? (int64_t)ld : (int64_t)(4 * W);
   constexpr int G = 32 / W;
   constexpr int T = 32;
   constexpr int BATCH = U * G;
@@ -1547,20 +1548,29 @@ int hpspmm_spmm_coo_f32(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_
   const int64_t blocks = (n_workers + kBlockThreads / 32 - 1) / (kBlockThreads / 32);
   if (blocks > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-  if (K == 32 || K == 64 || K == 128) {
+  if (K % 32 == 0 && K <= 512) {
+    // 32/64/128 directly, other multiples of 32 as column slabs of 128, 64 and 32 (every slab accumulates into
+    // its own columns of C, so the slabs are independent)
     int32_t Sw = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
     Sw = (Sw + 31) / 32 * 32;
     constexpr int BT = 64;
     const int64_t n_w = (nnz_padded + Sw - 1) / Sw;
     const int64_t nb = (n_w + BT / 32 - 1) / (BT / 32);
     if (nb > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
-    if (K == 32)
-      spmm_coo_warp_kernel<8, 4, BT><<<(unsigned)nb, BT, 0, s>>>(nnz_padded, Sw, row_idx, col_idx, vals, B, C);
-    else if (K == 64)
-      spmm_coo_warp_kernel<16, 4, BT><<<(unsigned)nb, BT, 0, s>>>(nnz_padded, Sw, row_idx, col_idx, vals, B, C);
-    else
-      spmm_coo_warp_kernel<32, 4, BT><<<(unsigned)nb, BT, 0, s>>>(nnz_padded, Sw, row_idx, col_idx, vals, B, C);
-    ctx->launches++;
+    const bool whole = K == 32 || K == 64 || K == 128;
+    int64_t off = 0;
+    while (off < K) {
+      const int64_t w = K - off >= 128 ? 128 : (K - off >= 64 ? 64 : 32);
+#define HPSPMM_COO(WW, ST) \
+  spmm_coo_warp_kernel<WW, 4, BT, ST><<<(unsigned)nb, BT, 0, s>>>(nnz_padded, Sw, row_idx, col_idx, vals, B + off, \
+                                                                 C + off, (int)K)
+      if (w == 128) { if (whole) HPSPMM_COO(32, false); else HPSPMM_COO(32, true); }
+      else if (w == 64) { if (whole) HPSPMM_COO(16, false); else HPSPMM_COO(16, true); }
+      else { if (whole) HPSPMM_COO(8, false); else HPSPMM_COO(8, true); }
+#undef HPSPMM_COO
+      ctx->launches++;
+      off += w;
+    }
     HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
     return HPSPMM_OK;
   }

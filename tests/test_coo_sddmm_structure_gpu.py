@@ -7,7 +7,7 @@ from helpers import check_against_f64, guarded_output, random_csr
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("K", [32, 64, 128, 20, 7, 640])
+@pytest.mark.parametrize("K", [32, 64, 128, 20, 7, 640, 96, 160, 256, 512])
 def test_coo_accumulates_like_lbspmm(gpu_ctx, pkg, oracle, K):
     ctx = gpu_ctx
     g = pkg.gen_rmat(11, 16, seed=5)
@@ -55,7 +55,7 @@ def test_coo_reordered_rows_and_nan_in_padding_row(gpu_ctx, pkg, oracle):
         b.free()
 
 
-@pytest.mark.parametrize("K", [32, 64, 128, 48])
+@pytest.mark.parametrize("K", [32, 64, 128, 48, 224])
 @pytest.mark.parametrize("order", ["shuffled", "heavy_rows", "padded_inside"])
 def test_coo_triples_in_any_order(gpu_ctx, pkg, oracle, K, order):
     """The COO contract puts no order on the triples: entries of one row scattered over many chunks, runs of
