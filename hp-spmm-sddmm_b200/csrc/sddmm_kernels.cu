@@ -73,14 +73,16 @@ __device__ __forceinline__ void reduce4_transposed(float (&p)[4], int lane) {
   }
 }
 
-template <int W, bool HINT, int BT>
+// SLAB = 0: X and Y are 4 * W columns wide.  SLAB = 1 / 2: the kernel covers a slab of 4 * W columns of wider
+// X and Y (row stride ld); 1 writes the partial dot products, 2 adds them to what earlier slabs wrote.
+template <int W, bool HINT, int BT, int SLAB>
 __global__ void __launch_bounds__(BT)
 sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
                   const int* __restrict__ col_idx, const float* __restrict__ X,
                   const float* __restrict__ Y, float* __restrict__ out,
                   const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
-                  const int* __restrict__ chunk_order) {
-  constexpr int K = 4 * W;
+                  const int* __restrict__ chunk_order, int ld) {
+  const int64_t K = SLAB ? (int64_t)ld : (int64_t)(4 * W);
   constexpr int G = 32 / W;
   constexpr int T = 32;
   constexpr int U = 4;
@@ -180,7 +182,7 @@ sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
       if (W >= 32) total += __shfl_xor_sync(0xffffffffu, total, 16);
       const int slot = ((l & 1) << 1) | ((l >> 1) & 1);   // which of the U entries lane l holds
       const int j = j0 + slot * G + g;
-      if (l < 4 && j < n1) out[j] = total;
+      if (l < 4 && j < n1) out[j] = SLAB == 2 ? out[j] + total : total;
     }
     __syncwarp();
     stage_tile(stage, base + STAGES * T);
@@ -225,20 +227,19 @@ sddmm_generic_kernel(int M, int K, int n_chunks, const int* __restrict__ row_ptr
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-template <int W, int R>
+template <int W, int SLAB>
 void launch_sddmm(bool hint, int M, int n_chunks, const int32_t* row_ptr, const int32_t* col_idx,
                   const float* X, const float* Y, float* out, const int32_t* chunk_start,
-                  const int32_t* chunk_row, const int32_t* chunk_order, cudaStream_t s) {
-  static_assert(R == 1, "the warp kernel keeps one float4 per lane");
+                  const int32_t* chunk_row, const int32_t* chunk_order, cudaStream_t s, int ld = 4 * W) {
   constexpr int BT = 64;
   const int cpb = BT / 32;
   const unsigned grid = (unsigned)((n_chunks + cpb - 1) / cpb);
   if (hint)
-    sddmm_warp_kernel<W, true, BT><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
-                                                       chunk_start, chunk_row, chunk_order);
+    sddmm_warp_kernel<W, true, BT, SLAB><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
+                                                             chunk_start, chunk_row, chunk_order, ld);
   else
-    sddmm_warp_kernel<W, false, BT><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
-                                                        chunk_start, chunk_row, chunk_order);
+    sddmm_warp_kernel<W, false, BT, SLAB><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
+                                                              chunk_start, chunk_row, chunk_order, ld);
 }
 
 }  // namespace
@@ -297,11 +298,30 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
   }
   const int m = (int)M, nc = (int)n_chunks;
   if (K == 32) {
-    launch_sddmm<8, 1>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
+    launch_sddmm<8, 0>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
   } else if (K == 64) {
-    launch_sddmm<16, 1>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
+    launch_sddmm<16, 0>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
   } else if (K == 128) {
-    launch_sddmm<32, 1>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
+    launch_sddmm<32, 0>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
+  } else if (K % 32 == 0 && K <= 512) {
+    // other multiples of 32: column slabs of 128, 64 and 32; the first writes, the others add their share
+    int64_t off = 0;
+    while (off < K) {
+      const int64_t w = K - off >= 128 ? 128 : (K - off >= 64 ? 64 : 32);
+#define HPSPMM_SDDMM(WW)                                                                                  \
+  if (off == 0)                                                                                           \
+    launch_sddmm<WW, 1>(hint, m, nc, row_ptr, col_idx, X + off, Y + off, out_vals, chunk_start, chunk_row, \
+                        chunk_order, s, (int)K);                                                          \
+  else                                                                                                    \
+    launch_sddmm<WW, 2>(hint, m, nc, row_ptr, col_idx, X + off, Y + off, out_vals, chunk_start, chunk_row, \
+                        chunk_order, s, (int)K)
+      if (w == 128) { HPSPMM_SDDMM(32); }
+      else if (w == 64) { HPSPMM_SDDMM(16); }
+      else { HPSPMM_SDDMM(8); }
+#undef HPSPMM_SDDMM
+      off += w;
+      if (off < K) ctx->launches++;
+    }
   } else {
     const unsigned grid = (unsigned)((n_chunks + kBlockThreads / 32 - 1) / (kBlockThreads / 32));
     if ((K & 3) == 0)

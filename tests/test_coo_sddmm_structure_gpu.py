@@ -91,7 +91,7 @@ def test_coo_triples_in_any_order(gpu_ctx, pkg, oracle, K, order):
         b.free()
 
 
-@pytest.mark.parametrize("K", [32, 64, 128, 4, 20, 33, 200, 1])
+@pytest.mark.parametrize("K", [32, 64, 128, 4, 20, 33, 200, 1, 96, 160, 256, 512])
 @pytest.mark.parametrize("use_plan", [False, True])
 def test_sddmm(gpu_ctx, pkg, oracle, K, use_plan):
     ctx = gpu_ctx
