@@ -122,3 +122,37 @@ def test_cfg5_gnn_layer_full_size(gpu_ctx, pkg, oracle):
     ctx.plan_destroy(plan_t)
     for b in (d_rp, d_ci, d_v, d_H, d_dC, d_C, d_dA, d_rpt, d_cit, d_vt, d_dH):
         b.free()
+
+
+def test_cfg2_graph_at_k256_runs_as_two_slabs(gpu_ctx, pkg, oracle):
+    """The R-MAT scale-20 graph at K = 256 (two strided 128-column slabs): the product against the oracle, the COO
+    product and the SDDMM on the same operands."""
+    ctx = gpu_ctx
+    K = 256
+    g = pkg.gen_rmat(20, 16, seed=2)
+    M, N, nnz = g["M"], g["N"], g["nnz"]
+    B = pkg.host_fill_uniform(N * K, 2, 256, -1.0, 1.0).reshape(N, K)
+    d_rp, d_ci, d_v, d_B = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"]), ctx.upload(g["vals"]), ctx.upload(B)
+    d_C = ctx.alloc((M, K), np.float32)
+    plan = ctx.plan_create(M, nnz, d_rp, K, N=N, col_idx=d_ci)
+    ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_B, d_C, plan=plan)
+    ref, abs_sum = oracle.spmm_f64(g["row_ptr"], g["col_idx"], g["vals"], B)
+    check_against_f64(d_C.to_host(), ref, abs_sum, "K=256 CSR")
+    # COO contract on the same graph: zero C, accumulate once
+    padded = (nnz + 31) // 32 * 32
+    d_r, d_c, d_w = ctx.alloc((padded,), np.int32), ctx.alloc((padded,), np.int32), ctx.alloc((padded,), np.float32)
+    ctx.csr_to_coo_padded(M, nnz, d_rp, d_ci, d_v, 32, d_r, d_c, d_w)
+    ctx.fill(d_C, M * K, 0.0)
+    ctx.spmm_coo(M, N, K, padded, d_r, d_c, d_w, d_B, d_C)
+    check_against_f64(d_C.to_host(), ref, abs_sum, "K=256 COO")
+    del ref, abs_sum
+    # SDDMM with X = a second dense matrix
+    X = pkg.host_fill_uniform(M * K, 2, 257, -1.0, 1.0).reshape(M, K)
+    d_X = ctx.upload(X)
+    d_o = ctx.alloc((nnz,), np.float32)
+    ctx.sddmm_csr(M, N, K, nnz, d_rp, d_ci, d_X, d_B, d_o, plan=plan)
+    ref, abs_sum = oracle.sddmm_f64(g["row_ptr"], g["col_idx"], X, B)
+    check_against_f64(d_o.to_host(), ref, abs_sum, "K=256 SDDMM")
+    ctx.plan_destroy(plan)
+    for b in (d_rp, d_ci, d_v, d_B, d_C, d_r, d_c, d_w, d_X, d_o):
+        b.free()
