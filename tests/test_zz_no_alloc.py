@@ -23,7 +23,7 @@ def _static_call(pkg, M, N, K, nnz, d_rp, d_ci, d_v, d_B, c_ptr):
     return st, err.value.decode()
 
 
-@pytest.mark.parametrize("K", [32, 128, 20])
+@pytest.mark.parametrize("K", [32, 128, 20, 96])
 def test_static_scratch_matches_ordinary_entry_twice(gpu_ctx, pkg, oracle, K):
     ctx = gpu_ctx
     g = pkg.gen_rmat(13, 16, seed=12)          # heavy rows: the carry slots are exercised
