@@ -94,9 +94,11 @@ int32_t hpspmm_default_chunk_nnz(int64_t K);
 
 // Builds chunk_start / chunk_row for (M, nnz, row_ptr) into the given arrays (device).
 // split_count (device int, may be null) receives the number of chunks ending mid-row.
+// run_counter (n_chunks + 1 ints, may be null) is zeroed.
 int hpspmm_launch_chunk_table(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
                               int32_t chunk_nnz, int64_t n_chunks, int32_t* chunk_start,
-                              int32_t* chunk_row, int* split_count, cudaStream_t stream);
+                              int32_t* chunk_row, int* split_count, cudaStream_t stream,
+                              int32_t* run_counter);
 
 // Processing order of the chunks: chunk ids sorted by estimated cost (entries / 8 + rows / 2),
 // most expensive first (stable 8-bit counting-sort passes on the device).  Chunks full of short

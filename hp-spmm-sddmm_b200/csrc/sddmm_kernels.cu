@@ -287,7 +287,7 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
     int32_t* cs = (int32_t*)ctx->scratch;
     int32_t* cr = (int32_t*)((char*)ctx->scratch + b_int);
     int32_t* co = (int32_t*)((char*)ctx->scratch + 2 * b_int);
-    st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, cs, cr, nullptr, s);
+    st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, cs, cr, nullptr, s, nullptr);
     if (st != HPSPMM_OK) return st;
     st = hpspmm_order_chunks_by_cost(ctx, M, N, n_chunks, row_ptr, nullptr, cs, cr, co,
                                      (char*)ctx->scratch + 3 * b_int, s);

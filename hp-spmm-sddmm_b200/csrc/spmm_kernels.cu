@@ -34,9 +34,11 @@ constexpr int kBlockThreads = 256;
 
 __global__ void chunk_table_kernel(int M, int nnz, const int* __restrict__ row_ptr, int S,
                                    int n_chunks, int* __restrict__ chunk_start,
-                                   int* __restrict__ chunk_row, int* __restrict__ split_count) {
+                                   int* __restrict__ chunk_row, int* __restrict__ split_count,
+                                   int* __restrict__ run_counter) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c > n_chunks) return;
+  if (run_counter != nullptr) run_counter[c] = 0;   // per-row counters of the in-kernel carry settlement
   if (c == n_chunks) {
     chunk_start[c] = nnz;
     return;
@@ -1119,10 +1121,11 @@ int32_t hpspmm_default_chunk_nnz(int64_t K) {
 
 int hpspmm_launch_chunk_table(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
                               int32_t chunk_nnz, int64_t n_chunks, int32_t* chunk_start,
-                              int32_t* chunk_row, int* split_count, cudaStream_t stream) {
+                              int32_t* chunk_row, int* split_count, cudaStream_t stream,
+                              int32_t* run_counter) {
   const unsigned blocks = (unsigned)((n_chunks + 1 + 255) / 256);
-  chunk_table_kernel<<<blocks, 256, 0, stream>>>((int)M, (int)nnz, row_ptr, chunk_nnz,
-                                                 (int)n_chunks, chunk_start, chunk_row, split_count);
+  chunk_table_kernel<<<blocks, 256, 0, stream>>>((int)M, (int)nnz, row_ptr, chunk_nnz, (int)n_chunks,
+                                                 chunk_start, chunk_row, split_count, run_counter);
   ctx->launches++;
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;
@@ -1299,7 +1302,7 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const
   if (e == cudaSuccess) e = cudaMemsetAsync(p->run_counter, 0, b_count, s);
   if (e == cudaSuccess && M > 0)
     st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, p->n_chunks, p->chunk_start,
-                                   p->chunk_row, ctx->flag, s);
+                                   p->chunk_row, ctx->flag, s, nullptr);
   if (e == cudaSuccess && st == HPSPMM_OK && M > 0)
     st = hpspmm_order_chunks_by_cost(ctx, M, N, p->n_chunks, row_ptr, col_idx, p->chunk_start, p->chunk_row,
                                      p->chunk_order, sort_scratch, s);
@@ -1375,24 +1378,26 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
   const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
   const size_t b_cval = align_up((size_t)(n_chunks + 1) * (size_t)K * 4, 256);
   const size_t b_sort = hpspmm_order_scratch_bytes(n_chunks);
-  st = hpspmm_ensure_scratch(ctx, 4 * b_int + b_cval + b_sort);
+  st = hpspmm_ensure_scratch(ctx, 5 * b_int + b_cval + b_sort);
   if (st != HPSPMM_OK) return st;
   char* base = (char*)ctx->scratch;
   int32_t* chunk_start = (int32_t*)base;
   int32_t* chunk_row = (int32_t*)(base + b_int);
   int32_t* carry_row = (int32_t*)(base + 2 * b_int);
   int32_t* chunk_order = (int32_t*)(base + 3 * b_int);
-  float* carry_val = (float*)(base + 4 * b_int);
-  void* sort_scratch = base + 4 * b_int + b_cval;
+  int32_t* run_counter = (int32_t*)(base + 4 * b_int);
+  float* carry_val = (float*)(base + 5 * b_int);
+  void* sort_scratch = base + 5 * b_int + b_cval;
+  // the table kernel also zeroes the counters of the in-kernel carry settlement
   st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, chunk_start, chunk_row,
-                                 nullptr, s);
+                                 nullptr, s, run_counter);
   if (st != HPSPMM_OK) return st;
   // cost order only: the second sort pass of the column-band order costs more per call than it saves
   st = hpspmm_order_chunks_by_cost(ctx, M, N, n_chunks, row_ptr, nullptr, chunk_start, chunk_row, chunk_order,
                                    sort_scratch, s);
   if (st != HPSPMM_OK) return st;
   return run_spmm(ctx, hint, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
-                  chunk_row, carry_row, carry_val, chunk_order, true, s, S);
+                  chunk_row, carry_row, carry_val, chunk_order, true, s, S, run_counter);
 }
 
 // Host-buffer product, pipelined over 32-column slabs when K is a multiple of 32 and K >= 64:
@@ -1423,7 +1428,7 @@ static int host_product_slabs(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, 
     const int32_t S = (opts && opts->chunk_nnz > 0) ? (opts->chunk_nnz + 31) / 32 * 32 : hpspmm_default_chunk_nnz(KS);
     const int64_t n_chunks = (nnz + S - 1) / S;
     const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
-    st = hpspmm_ensure_scratch(ctx, 4 * b_int + align_up((size_t)(n_chunks + 1) * KS * 4, 256) +
+    st = hpspmm_ensure_scratch(ctx, 5 * b_int + align_up((size_t)(n_chunks + 1) * KS * 4, 256) +
                                         hpspmm_order_scratch_bytes(n_chunks));
     if (st != HPSPMM_OK) return st;
   }
@@ -1653,10 +1658,10 @@ extern "C" int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M,
   const int64_t n_chunks = (nnz + S - 1) / S;
   const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
   const size_t b_cval = align_up((size_t)(n_chunks + 1) * (size_t)K * 4, 256);
-  const size_t need = 3 * b_int + b_cval;
+  const size_t need = 4 * b_int + b_cval;
   if (need > (size_t)HPSPMM_STATIC_SCRATCH_BYTES) {
     char msg[256];
-    const long long max_chunks = (long long)(HPSPMM_STATIC_SCRATCH_BYTES - 4 * 256) / (12 + 4 * K) - 1;
+    const long long max_chunks = (long long)(HPSPMM_STATIC_SCRATCH_BYTES - 5 * 256) / (16 + 4 * K) - 1;
     snprintf(msg, sizeof(msg),
              "matrix too large for the static scratch: nnz = %lld at K = %lld needs %zu bytes, the "
              "array holds %u (about %lld nnz at this K); use hpspmm_spmm_csr_f32 instead",
@@ -1694,19 +1699,20 @@ extern "C" int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M,
   }
   local.sm_count = state.sm_count;
 
-  // Every call rewrites the whole chunk table and every carry_row entry it later reads, and
-  // a carry_val slot is read only where this call's carry_row names a row, so nothing left
-  // over from an earlier call is ever consumed and nothing needs clearing first.
+  // Every call rewrites the whole chunk table, zeroes the per-row counters (the table kernel does
+  // both) and rewrites every carry_row entry it later reads, and a carry_val slot is read only
+  // where this call hands a carry on, so nothing left over from an earlier call is ever consumed.
   int32_t* chunk_start = (int32_t*)state.base;
   int32_t* chunk_row = (int32_t*)(state.base + b_int);
   int32_t* carry_row = (int32_t*)(state.base + 2 * b_int);
-  float* carry_val = (float*)(state.base + 3 * b_int);
+  int32_t* run_counter = (int32_t*)(state.base + 3 * b_int);
+  float* carry_val = (float*)(state.base + 4 * b_int);
   cudaStream_t s = (cudaStream_t)stream;
   st = hpspmm_launch_chunk_table(&local, M, nnz, row_ptr, S, n_chunks, chunk_start, chunk_row,
-                                 nullptr, s);
+                                 nullptr, s, run_counter);
   if (st == HPSPMM_OK)
     st = run_spmm(&local, K >= 64, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
-                  chunk_row, carry_row, carry_val, /*chunk_order=*/nullptr, true, s, S);
+                  chunk_row, carry_row, carry_val, /*chunk_order=*/nullptr, true, s, S, run_counter);
   if (st != HPSPMM_OK) write_err(err_buf, err_len, local.err);
   return st;
 }

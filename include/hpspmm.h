@@ -166,11 +166,11 @@ HPSPMM_API int hpspmm_plan_tables(const hpspmm_plan* plan, const int32_t** chunk
  * cannot take the device-wide synchronisation an allocation may bring.
  *
  * This entry point calls no cudaMalloc, cudaFree or allocating library routine, and needs
- * no context.  The chunk table and the carry slots of the nnz-balanced kernel live in one
- * 16 MiB array inside the library image, so every GPU that loads the library gives up
+ * no context.  The chunk table, the carry slots and the per-row counters of the nnz-balanced
+ * kernel live in one 16 MiB array inside the library image, so every GPU that loads the library gives up
  * 16 MiB until the process exits.  A matrix whose scratch would not fit -- more than
- * (16 MiB - 1 KiB) / (12 + 4 K) chunks (of 128 / 160 / 256 nnz at K = 32 / 64 / 128): about 15 M nnz at K = 32, 10 M at
- * K = 64, 8 M at K = 128 -- is refused with HPSPMM_ERR_UNSUPPORTED and a message in
+ * (16 MiB - 1.25 KiB) / (16 + 4 K) chunks (of 128 / 160 / 256 nnz at K = 32 / 64 / 128):
+ * about 15 M nnz at K = 32, 10 M at K = 64, 8 M at K = 128 -- is refused with HPSPMM_ERR_UNSUPPORTED and a message in
  * err_buf; use hpspmm_spmm_csr_f32 for it.
  *
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress,
