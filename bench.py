@@ -296,7 +296,12 @@ def main():
 
     t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
     nnz_all = torch.tensor([float(nnz_l)], dtype=torch.float64, device=dev)
+    per_rank_ms = [total_ms / args.steps]
     if n_gpus > 1:
+        mine = t.clone()
+        every = [torch.zeros_like(mine) for _ in range(n_gpus)]
+        dist.all_gather(every, mine)
+        per_rank_ms = [float(x.item()) / args.steps for x in every]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(nnz_all, op=dist.ReduceOp.SUM)
     max_ms = float(t.item())
@@ -421,7 +426,8 @@ def main():
                        "empty_rows": info["empty_rows"], "n_ref_rank0": n_ref,
                        "plan": plan_info, "l2": "operands larger than L2 (no flush)",
                        "b": "all-gathered per step (NCCL)" if b_sharded else "replicated",
-                       "parallelism": "row-shard x%d" % n_gpus},
+                       "parallelism": "row-shard x%d" % n_gpus,
+                       "per_rank_ms_per_step": [round(x, 4) for x in per_rank_ms]},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "comparisons": compare,
             "clocks": clocks,
