@@ -55,19 +55,20 @@ def load_peak():
 
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
-        self.index = index
+    def __init__(self, indices):
+        """indices: the GPUs of all ranks, this rank's own first."""
+        self.indices = list(indices)
         self.proc = None
         self.lines = []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                ["nvidia-smi", "-i", ",".join(str(i) for i in self.indices), "--query-gpu=" + self.FIELDS,
                  "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
@@ -87,23 +88,29 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, smmax, reasons = [], [], set()
+        sm, smmax, reasons, per_gpu = [], [], set(), {}
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
-            if len(f) < 7:
+            if len(f) < 8:
                 continue
             try:
-                sm.append(float(f[0]))
-                smmax.append(float(f[1]))
+                idx, mhz, mx = int(f[0]), float(f[1]), float(f[2])
             except ValueError:
                 continue
-            for n, v in zip(names, f[3:7]):
+            per_gpu.setdefault(idx, []).append(mhz)
+            smmax.append(mx)
+            if idx == self.indices[0]:
+                sm.append(mhz)
+            for n, v in zip(names, f[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(smmax) if smmax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        out = {"sm_mhz": statistics.median(sm) if sm else None,
+               "sm_max_mhz": max(smmax) if smmax else None,
+               "samples": len(sm), "reasons": sorted(reasons)}
+        if len(per_gpu) > 1:
+            out["per_gpu_sm_mhz"] = {str(i): statistics.median(v) for i, v in sorted(per_gpu.items())}
+        return out
 
 
 def build_workload(pkg, n_gpus, rank):
@@ -272,8 +279,10 @@ def main():
     per_k_events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                      for _ in ks] for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
-                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    phys = [int(x) for x in visible.split(",")] if visible else list(range(max(n_gpus, local_rank + 1)))
+    mine = phys[local_rank] if local_rank < len(phys) else local_rank
+    sampler = ClockSampler([mine] + [p for p in phys[:n_gpus] if p != mine])
     launches_before = ctx.launch_count()
     if rank == 0:
         sampler.start()
@@ -286,12 +295,14 @@ def main():
     barrier()
     launches = ctx.launch_count() - launches_before
     total_ms = e0.elapsed_time(e1)
-    # keep the GPU busy a little longer so the clock sampler sees the loaded state
-    if rank == 0:
-        t_end = time.time() + 0.5
-        while time.time() < t_end:
-            step(collective=False)   # rank 0 alone: no collective here
-        torch.cuda.synchronize()
+    # keep every GPU busy a little longer so the clock sampler (rank 0 watches all of them) sees the
+    # loaded state; each rank loops on its own, so no collective here
+    t_end = time.time() + 0.5
+    while time.time() < t_end:
+        step(collective=False)
+    torch.cuda.synchronize()
+    if n_gpus > 1:
+        dist.barrier()   # every GPU stays loaded until the sampler is stopped
     clocks = sampler.stop() if rank == 0 else None
 
     t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
