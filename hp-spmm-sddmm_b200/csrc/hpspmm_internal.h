@@ -46,6 +46,11 @@ struct hpspmm_plan {
   int32_t* carry_row;
   float* carry_val;
   int32_t* run_counter;  // one per chunk, zero between launches: pieces of a split row that have finished
+  // rows that hold entries: ids (ascending, then the sentinel M), their ends in the entry array, and
+  // for every chunk the position in this list of the row holding its first entry
+  int32_t* nz_id;
+  int32_t* nz_end;
+  int32_t* chunk_ri;
   size_t bytes;
 };
 
@@ -111,6 +116,13 @@ int hpspmm_order_chunks_by_cost(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t n
                                 const int32_t* row_ptr, const int32_t* col_idx, const int32_t* chunk_start,
                                 const int32_t* chunk_row, int32_t* order_out, void* scratch,
                                 cudaStream_t stream);
+
+// The rows that hold entries, as the product kernels of a plan walk them: nz_id / nz_end need M + 1
+// ints each, chunk_ri n_chunks; scratch needs hpspmm_row_list_scratch_bytes(M) bytes.
+size_t hpspmm_row_list_scratch_bytes(int64_t M);
+int hpspmm_build_row_list(hpspmm_ctx* ctx, int64_t M, int64_t n_chunks, const int32_t* row_ptr,
+                          const int32_t* chunk_row, int32_t* nz_id, int32_t* nz_end, int32_t* chunk_ri,
+                          void* scratch, cudaStream_t stream);
 
 // ---- counter-based PRNG shared by host and device --------------------------------------
 // splitmix64 finaliser over (seed, stream, index); 24 high bits -> [0, 1).

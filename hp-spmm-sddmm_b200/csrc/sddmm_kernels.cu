@@ -75,13 +75,16 @@ __device__ __forceinline__ void reduce4_transposed(float (&p)[4], int lane) {
 
 // SLAB = 0: X and Y are 4 * W columns wide.  SLAB = 1 / 2: the kernel covers a slab of 4 * W columns of wider
 // X and Y (row stride ld); 1 writes the partial dot products, 2 adds them to what earlier slabs wrote.
-template <int W, bool HINT, int BT, int SLAB>
+// COMPACT: the plan's list of rows that hold entries (nz_id, nz_end, chunk_ri) replaces the row-by-row probing
+// of row_ptr when a row ends.
+template <int W, bool HINT, int BT, int SLAB, bool COMPACT>
 __global__ void __launch_bounds__(BT)
 sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
                   const int* __restrict__ col_idx, const float* __restrict__ X,
                   const float* __restrict__ Y, float* __restrict__ out,
                   const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
-                  const int* __restrict__ chunk_order, int ld) {
+                  const int* __restrict__ chunk_order, int ld, const int* __restrict__ nz_id,
+                  const int* __restrict__ nz_end, const int* __restrict__ chunk_ri) {
   const int64_t K = SLAB ? (int64_t)ld : (int64_t)(4 * W);
   constexpr int G = 32 / W;
   constexpr int T = 32;
@@ -102,8 +105,9 @@ sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
 
   const int n0 = __ldg(chunk_start + chunk);
   const int n1 = __ldg(chunk_start + chunk + 1);
-  int row = __ldg(chunk_row + chunk);
-  int row_end = __ldg(row_ptr + row + 1);
+  int ri = COMPACT ? __ldg(chunk_ri + chunk) : 0;
+  int row = COMPACT ? __ldg(nz_id + ri) : __ldg(chunk_row + chunk);
+  int row_end = COMPACT ? __ldg(nz_end + ri) : __ldg(row_ptr + row + 1);
 
   auto stage_tile = [&](int stage, int base) {
     const int j = base + lane;
@@ -121,6 +125,13 @@ sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
 
   // entry `next_entry` starts a later row: find it and fetch its fragment of X
   auto next_x = [&](int next_entry) {
+    if (COMPACT) {
+      ++ri;
+      row = __ldg(nz_id + ri);
+      row_end = __ldg(nz_end + ri);
+      x = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row * K + l * 4));
+      return;
+    }
     int e, probes = 0;
     do {
       ++row;
@@ -227,19 +238,30 @@ sddmm_generic_kernel(int M, int K, int n_chunks, const int* __restrict__ row_ptr
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+struct sddmm_row_list {
+  const int32_t* nz_id;
+  const int32_t* nz_end;
+  const int32_t* chunk_ri;
+};
+
 template <int W, int SLAB>
 void launch_sddmm(bool hint, int M, int n_chunks, const int32_t* row_ptr, const int32_t* col_idx,
                   const float* X, const float* Y, float* out, const int32_t* chunk_start,
-                  const int32_t* chunk_row, const int32_t* chunk_order, cudaStream_t s, int ld = 4 * W) {
+                  const int32_t* chunk_row, const int32_t* chunk_order, cudaStream_t s, sddmm_row_list rows,
+                  int ld = 4 * W) {
   constexpr int BT = 64;
   const int cpb = BT / 32;
   const unsigned grid = (unsigned)((n_chunks + cpb - 1) / cpb);
-  if (hint)
-    sddmm_warp_kernel<W, true, BT, SLAB><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
-                                                             chunk_start, chunk_row, chunk_order, ld);
-  else
-    sddmm_warp_kernel<W, false, BT, SLAB><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,
-                                                              chunk_start, chunk_row, chunk_order, ld);
+#define HPSPMM_SDDMM_LAUNCH(H, CP)                                                                        \
+  sddmm_warp_kernel<W, H, BT, SLAB, CP><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,      \
+                                                            chunk_start, chunk_row, chunk_order, ld,      \
+                                                            rows.nz_id, rows.nz_end, rows.chunk_ri)
+  if (rows.nz_id != nullptr) {
+    if (hint) HPSPMM_SDDMM_LAUNCH(true, true); else HPSPMM_SDDMM_LAUNCH(false, true);
+  } else {
+    if (hint) HPSPMM_SDDMM_LAUNCH(true, false); else HPSPMM_SDDMM_LAUNCH(false, false);
+  }
+#undef HPSPMM_SDDMM_LAUNCH
 }
 
 }  // namespace
@@ -269,6 +291,7 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
   const int32_t* chunk_start;
   const int32_t* chunk_row;
   const int32_t* chunk_order = nullptr;
+  sddmm_row_list rows = {nullptr, nullptr, nullptr};
   int64_t n_chunks;
   if (plan) {
     HPSPMM_REQUIRE(ctx, plan->M == M && plan->nnz == nnz, "plan built for another matrix");
@@ -277,6 +300,7 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
     chunk_row = plan->chunk_row;
     chunk_order = plan->chunk_order;
     n_chunks = plan->n_chunks;
+    rows = sddmm_row_list{plan->nz_id, plan->nz_end, plan->chunk_ri};
   } else {
     int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
     S = (S + 31) / 32 * 32;
@@ -298,11 +322,11 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
   }
   const int m = (int)M, nc = (int)n_chunks;
   if (K == 32) {
-    launch_sddmm<8, 0>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
+    launch_sddmm<8, 0>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s, rows);
   } else if (K == 64) {
-    launch_sddmm<16, 0>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
+    launch_sddmm<16, 0>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s, rows);
   } else if (K == 128) {
-    launch_sddmm<32, 0>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s);
+    launch_sddmm<32, 0>(hint, m, nc, row_ptr, col_idx, X, Y, out_vals, chunk_start, chunk_row, chunk_order, s, rows);
   } else if (K % 32 == 0 && K <= 512) {
     // other multiples of 32: column slabs of 128, 64 and 32; the first writes, the others add their share
     int64_t off = 0;
@@ -311,10 +335,10 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
 #define HPSPMM_SDDMM(WW)                                                                                  \
   if (off == 0)                                                                                           \
     launch_sddmm<WW, 1>(hint, m, nc, row_ptr, col_idx, X + off, Y + off, out_vals, chunk_start, chunk_row, \
-                        chunk_order, s, (int)K);                                                          \
+                        chunk_order, s, rows, (int)K);                                                    \
   else                                                                                                    \
     launch_sddmm<WW, 2>(hint, m, nc, row_ptr, col_idx, X + off, Y + off, out_vals, chunk_start, chunk_row, \
-                        chunk_order, s, (int)K)
+                        chunk_order, s, rows, (int)K)
       if (w == 128) { HPSPMM_SDDMM(32); }
       else if (w == 64) { HPSPMM_SDDMM(16); }
       else { HPSPMM_SDDMM(8); }

@@ -341,14 +341,19 @@ __device__ __noinline__ void settle_split_row(int r, int r_end, int S, const int
   if (lane == 0) run_counter[first] = 0;   // ready for the next launch
 }
 
-template <int W, int U, int MINB, bool HINT, int BT, bool SETTLE, bool STRIDED>
+template <int W, int U, int MINB, bool HINT, int BT, bool SETTLE, bool STRIDED, bool COMPACT>
 __global__ void __launch_bounds__(BT, MINB)
 spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict__ row_ptr,
                  const int* __restrict__ col_idx, const float* __restrict__ vals,
                  const float* __restrict__ B, float* __restrict__ C,
                  const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
                  int* __restrict__ carry_row, float* __restrict__ carry_val,
-                 const int* __restrict__ chunk_order, int S, int* __restrict__ run_counter, int ld) {
+                 const int* __restrict__ chunk_order, int S, int* __restrict__ run_counter, int ld,
+                 const int* __restrict__ nz_id, const int* __restrict__ nz_end,
+                 const int* __restrict__ chunk_ri) {
+  // COMPACT: the plan lists the rows that hold entries (nz_id, with their ends nz_end) and the position in
+  // that list of every chunk's first row (chunk_ri), so the kernel steps from one such row to the next with
+  // two independent loads and never looks at an empty row.  Without the list it probes row_ptr row by row.
   // The kernel computes a slab of KW = 4 * W columns.  STRIDED: the slab is part of wider matrices, B, C
   // and the carry slots have row stride ld; otherwise the stride is the compile-time KW.
   constexpr int KW = 4 * W;
@@ -376,8 +381,9 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
 
   const int n0 = __ldg(chunk_start + chunk);
   const int n1 = __ldg(chunk_start + chunk + 1);
-  int row = __ldg(chunk_row + chunk);
-  int row_end = __ldg(row_ptr + row + 1);
+  int ri = COMPACT ? __ldg(chunk_ri + chunk) : 0;
+  int row = COMPACT ? __ldg(nz_id + ri) : __ldg(chunk_row + chunk);
+  int row_end = COMPACT ? __ldg(nz_end + ri) : __ldg(row_ptr + row + 1);
 
   auto stage_tile = [&](int stage, int base) {
     const int j = base + lane;
@@ -402,6 +408,12 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
     const float4 t = reduce_groups<W>(acc);
     if (g == 0) st_stream(C + (int64_t)row * K + l * 4, t);
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (COMPACT) {
+      ++ri;
+      row = __ldg(nz_id + ri);
+      row_end = __ldg(nz_end + ri);
+      return;
+    }
     int e, probes = 0;
     do {
       ++row;
@@ -1047,12 +1059,19 @@ int launch_balanced(hpspmm_ctx* ctx, bool hint, bool rowsplit, int M, int n_chun
   return HPSPMM_OK;
 }
 
+// rows that hold entries, as a plan lists them (all null without a plan)
+struct row_list {
+  const int32_t* nz_id;
+  const int32_t* nz_end;
+  const int32_t* chunk_ri;
+};
+
 template <int W, int U, int MINB, int BT = kBlockThreads, bool STRIDED = false>
 int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* row_ptr,
                 const int32_t* col_idx, const float* vals, const float* B, float* C,
                 const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
                 float* carry_val, const int32_t* chunk_order, int S, int* run_counter, cudaStream_t stream,
-                int ld = 4 * W) {
+                int ld = 4 * W, row_list rows = row_list{nullptr, nullptr, nullptr}) {
   const int chunks_per_block = BT / 32;
   const int n_chunk_blocks = (n_chunks + chunks_per_block - 1) / chunks_per_block;
   int n_zero_blocks = (M + BT - 1) / BT;
@@ -1060,14 +1079,17 @@ int launch_warp(hpspmm_ctx* ctx, bool hint, int M, int n_chunks, const int32_t* 
   if (n_zero_blocks > cap) n_zero_blocks = cap;
   const unsigned grid = (unsigned)(n_chunk_blocks + n_zero_blocks);
   if (grid == 0) return HPSPMM_OK;
-#define HPSPMM_LAUNCH_WARP(H, ST)                                                               \
-  spmm_warp_kernel<W, U, MINB, H, BT, ST, STRIDED><<<grid, BT, 0, stream>>>(                       \
+#define HPSPMM_LAUNCH_WARP(H, ST, CP)                                                           \
+  spmm_warp_kernel<W, U, MINB, H, BT, ST, STRIDED, CP><<<grid, BT, 0, stream>>>(                   \
       M, n_chunks, n_chunk_blocks, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, \
-      carry_val, chunk_order, S, run_counter, ld)
+      carry_val, chunk_order, S, run_counter, ld, rows.nz_id, rows.nz_end, rows.chunk_ri)
+  const bool compact = rows.nz_id != nullptr;
   if (run_counter != nullptr) {
-    if (hint) HPSPMM_LAUNCH_WARP(true, true); else HPSPMM_LAUNCH_WARP(false, true);
+    if (hint) { if (compact) HPSPMM_LAUNCH_WARP(true, true, true); else HPSPMM_LAUNCH_WARP(true, true, false); }
+    else { if (compact) HPSPMM_LAUNCH_WARP(false, true, true); else HPSPMM_LAUNCH_WARP(false, true, false); }
   } else {
-    if (hint) HPSPMM_LAUNCH_WARP(true, false); else HPSPMM_LAUNCH_WARP(false, false);
+    if (hint) { if (compact) HPSPMM_LAUNCH_WARP(true, false, true); else HPSPMM_LAUNCH_WARP(true, false, false); }
+    else { if (compact) HPSPMM_LAUNCH_WARP(false, false, true); else HPSPMM_LAUNCH_WARP(false, false, false); }
   }
 #undef HPSPMM_LAUNCH_WARP
   ctx->launches++;
@@ -1167,14 +1189,14 @@ template <int W, bool STRIDED>
 int run_slab(hpspmm_ctx* ctx, bool hint, int m, int nc, const int32_t* row_ptr, const int32_t* col_idx,
              const float* vals, const float* B, float* C, const int32_t* chunk_start,
              const int32_t* chunk_row, int32_t* carry_row, float* carry_val, const int32_t* chunk_order,
-             bool need_fixup, cudaStream_t stream, int S, int* run_counter, int ld) {
+             bool need_fixup, cudaStream_t stream, int S, int* run_counter, int ld, row_list rows) {
   const bool settle = run_counter != nullptr && W >= 16;
   // strided slabs carry two more live values (the stride) and spill at 48 registers: 16 blocks per SM
   // (64 registers) took the K = 256 product from 1.44 to 1.20 ms
   constexpr int MINB = STRIDED ? 16 : 20;
   int st = launch_warp<W, 4, MINB, 64, STRIDED>(ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start,
                                                 chunk_row, carry_row, carry_val, chunk_order, S,
-                                                settle ? run_counter : nullptr, stream, ld);
+                                                settle ? run_counter : nullptr, stream, ld, rows);
   if (st != HPSPMM_OK) return st;
   if (need_fixup && nc > 0 && !settle) {
     if (S > 0) {
@@ -1195,13 +1217,13 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
              const int32_t* row_ptr, const int32_t* col_idx, const float* vals, const float* B,
              float* C, const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
              float* carry_val, const int32_t* chunk_order, bool need_fixup, cudaStream_t stream,
-             int S = 0, int* run_counter = nullptr) {
+             int S = 0, int* run_counter = nullptr, row_list rows = row_list{nullptr, nullptr, nullptr}) {
   int st;
   const int m = (int)M, nc = (int)n_chunks;
 #define HPSPMM_ARGS ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, stream
 #define HPSPMM_SLAB(W, STRIDED, off) \
   run_slab<W, STRIDED>(ctx, hint, m, nc, row_ptr, col_idx, vals, B + (off), C + (off), chunk_start, chunk_row, \
-                       carry_row, carry_val + (off), chunk_order, need_fixup, stream, S, run_counter, (int)K)
+                       carry_row, carry_val + (off), chunk_order, need_fixup, stream, S, run_counter, (int)K, rows)
   if (rowsplit && (K == 32 || K == 64 || K == 128)) {
     st = K == 32 ? launch_balanced<8, 1, 8, 4>(HPSPMM_ARGS)
                  : (K == 64 ? launch_balanced<16, 1, 8, 4>(HPSPMM_ARGS) : launch_balanced<32, 1, 8, 4>(HPSPMM_ARGS));
@@ -1280,8 +1302,10 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const
   const size_t b_cval = align_up((size_t)(p->n_chunks + 1) * (size_t)max_K * 4, 256);
   const size_t b_order = align_up((size_t)(p->n_chunks + 1) * 4, 256);
   const size_t b_count = align_up((size_t)(p->n_chunks + 1) * 4, 256);
+  const size_t b_nz = align_up((size_t)(M + 2) * 4, 256);          // nz_id, nz_end: one slot per row + sentinel
+  const size_t b_ri = align_up((size_t)(p->n_chunks + 1) * 4, 256);
   const size_t b_sort = hpspmm_order_scratch_bytes(p->n_chunks);   // only needed while building
-  p->bytes = b_start + b_row + b_crow + b_cval + b_order + b_count + b_sort;
+  p->bytes = b_start + b_row + b_crow + b_cval + b_order + b_count + 2 * b_nz + b_ri + b_sort;
   char* base = nullptr;
   cudaError_t e = cudaMalloc((void**)&base, p->bytes);
   if (e != cudaSuccess) {
@@ -1294,7 +1318,10 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const
   p->carry_val = (float*)(base + b_start + b_row + b_crow);
   p->chunk_order = (int32_t*)(base + b_start + b_row + b_crow + b_cval);
   p->run_counter = (int32_t*)(base + b_start + b_row + b_crow + b_cval + b_order);
-  void* sort_scratch = base + b_start + b_row + b_crow + b_cval + b_order + b_count;
+  p->nz_id = (int32_t*)(base + b_start + b_row + b_crow + b_cval + b_order + b_count);
+  p->nz_end = (int32_t*)(base + b_start + b_row + b_crow + b_cval + b_order + b_count + b_nz);
+  p->chunk_ri = (int32_t*)(base + b_start + b_row + b_crow + b_cval + b_order + b_count + 2 * b_nz);
+  void* sort_scratch = base + b_start + b_row + b_crow + b_cval + b_order + b_count + 2 * b_nz + b_ri;
   cudaStream_t s = (cudaStream_t)stream;
   int st = HPSPMM_OK;
   int split = 0;
@@ -1306,6 +1333,13 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const
   if (e == cudaSuccess && st == HPSPMM_OK && M > 0)
     st = hpspmm_order_chunks_by_cost(ctx, M, N, p->n_chunks, row_ptr, col_idx, p->chunk_start, p->chunk_row,
                                      p->chunk_order, sort_scratch, s);
+  if (e == cudaSuccess && st == HPSPMM_OK && M > 0) {
+    // the list of rows that hold entries (its scratch lives in the context and is free again afterwards)
+    st = hpspmm_ensure_scratch(ctx, hpspmm_row_list_scratch_bytes(M));
+    if (st == HPSPMM_OK)
+      st = hpspmm_build_row_list(ctx, M, p->n_chunks, row_ptr, p->chunk_row, p->nz_id, p->nz_end, p->chunk_ri,
+                                 ctx->scratch, s);
+  }
   if (e == cudaSuccess && st == HPSPMM_OK)
     e = cudaMemcpyAsync(&split, ctx->flag, sizeof(int), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess && st == HPSPMM_OK) e = cudaStreamSynchronize(s);
@@ -1370,7 +1404,8 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
     HPSPMM_REQUIRE(ctx, plan->device == ctx->device, "plan built on another device");
     return run_spmm(ctx, hint, false, M, K, plan->n_chunks, row_ptr, col_idx, vals, B, C,
                     plan->chunk_start, plan->chunk_row, plan->carry_row, plan->carry_val,
-                    plan->chunk_order, plan->n_split_chunks > 0, s, plan->chunk_nnz, plan->run_counter);
+                    plan->chunk_order, plan->n_split_chunks > 0, s, plan->chunk_nnz, plan->run_counter,
+                    row_list{plan->nz_id, plan->nz_end, plan->chunk_ri});
   }
   int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
   S = (S + 31) / 32 * 32;

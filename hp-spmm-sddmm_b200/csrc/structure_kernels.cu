@@ -399,6 +399,60 @@ int build_ordered_row_ptr(hpspmm_ctx* ctx, int64_t M, const int32_t* row_ptr, co
 
 }  // namespace
 
+// ---- list of the rows that hold entries -------------------------------------------------------
+namespace {
+
+__global__ void nonempty_flag_kernel(int M, const int* __restrict__ row_ptr, int* __restrict__ flags) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r <= M; r += stride)
+    flags[r] = r < M ? (row_ptr[r + 1] > row_ptr[r] ? 1 : 0) : 0;
+}
+
+// rank[r] = number of rows before r that hold entries (rank[M] = their total)
+__global__ void row_list_scatter_kernel(int M, const int* __restrict__ row_ptr, const int* __restrict__ rank,
+                                        int* __restrict__ nz_id, int* __restrict__ nz_end) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r <= M; r += stride) {
+    if (r == M) {
+      // sentinel after the last row: never a row of C, an end no entry reaches
+      nz_id[rank[M]] = M;
+      nz_end[rank[M]] = 0x7fffffff;
+    } else if (row_ptr[r + 1] > row_ptr[r]) {
+      nz_id[rank[r]] = (int)r;
+      nz_end[rank[r]] = row_ptr[r + 1];
+    }
+  }
+}
+
+__global__ void chunk_row_index_kernel(int64_t n_chunks, const int* __restrict__ chunk_row,
+                                       const int* __restrict__ rank, int* __restrict__ chunk_ri) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += stride)
+    chunk_ri[c] = rank[chunk_row[c]];
+}
+
+}  // namespace
+
+size_t hpspmm_row_list_scratch_bytes(int64_t M) {
+  return align_up((size_t)(M + 1) * 4, 256) + align_up((size_t)((M + 1 + kScanTile - 1) / kScanTile + 1) * 4, 256);
+}
+
+int hpspmm_build_row_list(hpspmm_ctx* ctx, int64_t M, int64_t n_chunks, const int32_t* row_ptr,
+                          const int32_t* chunk_row, int32_t* nz_id, int32_t* nz_end, int32_t* chunk_ri,
+                          void* scratch, cudaStream_t stream) {
+  int* rank = (int*)scratch;
+  int* totals = (int*)((char*)scratch + align_up((size_t)(M + 1) * 4, 256));
+  nonempty_flag_kernel<<<grid_for(ctx, M + 1), kThreads, 0, stream>>>((int)M, row_ptr, rank);
+  ctx->launches++;
+  exclusive_scan_inplace(ctx, rank, M + 1, totals, stream);
+  row_list_scatter_kernel<<<grid_for(ctx, M + 1), kThreads, 0, stream>>>((int)M, row_ptr, rank, nz_id, nz_end);
+  if (n_chunks > 0)
+    chunk_row_index_kernel<<<grid_for(ctx, n_chunks), kThreads, 0, stream>>>(n_chunks, chunk_row, rank, chunk_ri);
+  ctx->launches += 2;
+  HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+  return HPSPMM_OK;
+}
+
 size_t hpspmm_order_scratch_bytes(int64_t n_chunks) {
   const int64_t n = n_chunks > 0 ? n_chunks : 1;
   const int64_t n_tiles = (n + kTile - 1) / kTile;
