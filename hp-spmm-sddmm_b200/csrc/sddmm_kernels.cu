@@ -306,16 +306,25 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
     S = (S + 31) / 32 * 32;
     n_chunks = (nnz + S - 1) / S;
     const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
-    int st = hpspmm_ensure_scratch(ctx, 3 * b_int + hpspmm_order_scratch_bytes(n_chunks));
+    const size_t b_nz = align_up((size_t)(M + 2) * 4, 256);
+    const size_t b_sort = hpspmm_order_scratch_bytes(n_chunks), b_list = hpspmm_row_list_scratch_bytes(M);
+    int st = hpspmm_ensure_scratch(ctx, 4 * b_int + 2 * b_nz + (b_sort > b_list ? b_sort : b_list));
     if (st != HPSPMM_OK) return st;
-    int32_t* cs = (int32_t*)ctx->scratch;
-    int32_t* cr = (int32_t*)((char*)ctx->scratch + b_int);
-    int32_t* co = (int32_t*)((char*)ctx->scratch + 2 * b_int);
+    char* sb = (char*)ctx->scratch;
+    int32_t* cs = (int32_t*)sb;
+    int32_t* cr = (int32_t*)(sb + b_int);
+    int32_t* co = (int32_t*)(sb + 2 * b_int);
+    int32_t* cri = (int32_t*)(sb + 3 * b_int);
+    int32_t* nzi = (int32_t*)(sb + 4 * b_int);
+    int32_t* nze = (int32_t*)(sb + 4 * b_int + b_nz);
+    void* tmp = sb + 4 * b_int + 2 * b_nz;
     st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, cs, cr, nullptr, s, nullptr);
     if (st != HPSPMM_OK) return st;
-    st = hpspmm_order_chunks_by_cost(ctx, M, N, n_chunks, row_ptr, nullptr, cs, cr, co,
-                                     (char*)ctx->scratch + 3 * b_int, s);
+    st = hpspmm_order_chunks_by_cost(ctx, M, N, n_chunks, row_ptr, nullptr, cs, cr, co, tmp, s);
     if (st != HPSPMM_OK) return st;
+    st = hpspmm_build_row_list(ctx, M, n_chunks, row_ptr, cr, nzi, nze, cri, tmp, s);
+    if (st != HPSPMM_OK) return st;
+    rows = sddmm_row_list{nzi, nze, cri};
     chunk_start = cs;
     chunk_row = cr;
     chunk_order = co;

@@ -1413,7 +1413,10 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
   const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
   const size_t b_cval = align_up((size_t)(n_chunks + 1) * (size_t)K * 4, 256);
   const size_t b_sort = hpspmm_order_scratch_bytes(n_chunks);
-  st = hpspmm_ensure_scratch(ctx, 5 * b_int + b_cval + b_sort);
+  const size_t b_nz = align_up((size_t)(M + 2) * 4, 256);
+  const size_t b_list = hpspmm_row_list_scratch_bytes(M);
+  const size_t b_tmp = b_sort > b_list ? b_sort : b_list;   // the two builders run one after the other
+  st = hpspmm_ensure_scratch(ctx, 6 * b_int + b_cval + 2 * b_nz + b_tmp);
   if (st != HPSPMM_OK) return st;
   char* base = (char*)ctx->scratch;
   int32_t* chunk_start = (int32_t*)base;
@@ -1421,18 +1424,26 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
   int32_t* carry_row = (int32_t*)(base + 2 * b_int);
   int32_t* chunk_order = (int32_t*)(base + 3 * b_int);
   int32_t* run_counter = (int32_t*)(base + 4 * b_int);
-  float* carry_val = (float*)(base + 5 * b_int);
-  void* sort_scratch = base + 5 * b_int + b_cval;
+  int32_t* chunk_ri = (int32_t*)(base + 5 * b_int);
+  float* carry_val = (float*)(base + 6 * b_int);
+  int32_t* nz_id = (int32_t*)(base + 6 * b_int + b_cval);
+  int32_t* nz_end = (int32_t*)(base + 6 * b_int + b_cval + b_nz);
+  void* tmp = base + 6 * b_int + b_cval + 2 * b_nz;
   // the table kernel also zeroes the counters of the in-kernel carry settlement
   st = hpspmm_launch_chunk_table(ctx, M, nnz, row_ptr, S, n_chunks, chunk_start, chunk_row,
                                  nullptr, s, run_counter);
   if (st != HPSPMM_OK) return st;
   // cost order only: the second sort pass of the column-band order costs more per call than it saves
   st = hpspmm_order_chunks_by_cost(ctx, M, N, n_chunks, row_ptr, nullptr, chunk_start, chunk_row, chunk_order,
-                                   sort_scratch, s);
+                                   tmp, s);
+  if (st != HPSPMM_OK) return st;
+  // the list of rows that hold entries: a few small launches per call, but without it a chunk in a very
+  // sparse region (entries separated by dozens of empty rows) can outlast the rest of the product
+  st = hpspmm_build_row_list(ctx, M, n_chunks, row_ptr, chunk_row, nz_id, nz_end, chunk_ri, tmp, s);
   if (st != HPSPMM_OK) return st;
   return run_spmm(ctx, hint, false, M, K, n_chunks, row_ptr, col_idx, vals, B, C, chunk_start,
-                  chunk_row, carry_row, carry_val, chunk_order, true, s, S, run_counter);
+                  chunk_row, carry_row, carry_val, chunk_order, true, s, S, run_counter,
+                  row_list{nz_id, nz_end, chunk_ri});
 }
 
 // Host-buffer product, pipelined over 32-column slabs when K is a multiple of 32 and K >= 64:
@@ -1463,8 +1474,9 @@ static int host_product_slabs(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, 
     const int32_t S = (opts && opts->chunk_nnz > 0) ? (opts->chunk_nnz + 31) / 32 * 32 : hpspmm_default_chunk_nnz(KS);
     const int64_t n_chunks = (nnz + S - 1) / S;
     const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
-    st = hpspmm_ensure_scratch(ctx, 5 * b_int + align_up((size_t)(n_chunks + 1) * KS * 4, 256) +
-                                        hpspmm_order_scratch_bytes(n_chunks));
+    const size_t b_sort = hpspmm_order_scratch_bytes(n_chunks), b_list = hpspmm_row_list_scratch_bytes(M);
+    st = hpspmm_ensure_scratch(ctx, 6 * b_int + align_up((size_t)(n_chunks + 1) * KS * 4, 256) +
+                                        2 * align_up((size_t)(M + 2) * 4, 256) + (b_sort > b_list ? b_sort : b_list));
     if (st != HPSPMM_OK) return st;
   }
   char* base = (char*)ctx->stage;
