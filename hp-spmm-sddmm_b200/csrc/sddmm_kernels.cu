@@ -75,9 +75,9 @@ __device__ __forceinline__ void reduce4_transposed(float (&p)[4], int lane) {
 
 // SLAB = 0: X and Y are 4 * W columns wide.  SLAB = 1 / 2: the kernel covers a slab of 4 * W columns of wider
 // X and Y (row stride ld); 1 writes the partial dot products, 2 adds them to what earlier slabs wrote.
-// COMPACT: the plan's list of rows that hold entries (nz_id, nz_end, chunk_ri) replaces the row-by-row probing
-// of row_ptr when a row ends.
-template <int W, bool HINT, int BT, int SLAB, bool COMPACT>
+// When a row ends the kernel steps to the next row that holds entries through the list nz_id / nz_end (chunk_ri:
+// position in that list of the row holding a chunk's first entry), so it never looks at an empty row.
+template <int W, bool HINT, int BT, int SLAB>
 __global__ void __launch_bounds__(BT)
 sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
                   const int* __restrict__ col_idx, const float* __restrict__ X,
@@ -105,9 +105,9 @@ sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
 
   const int n0 = __ldg(chunk_start + chunk);
   const int n1 = __ldg(chunk_start + chunk + 1);
-  int ri = COMPACT ? __ldg(chunk_ri + chunk) : 0;
-  int row = COMPACT ? __ldg(nz_id + ri) : __ldg(chunk_row + chunk);
-  int row_end = COMPACT ? __ldg(nz_end + ri) : __ldg(row_ptr + row + 1);
+  int ri = __ldg(chunk_ri + chunk);
+  int row = __ldg(nz_id + ri);
+  int row_end = __ldg(nz_end + ri);
 
   auto stage_tile = [&](int stage, int base) {
     const int j = base + lane;
@@ -125,31 +125,10 @@ sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
 
   // entry `next_entry` starts a later row: find it and fetch its fragment of X
   auto next_x = [&](int next_entry) {
-    if (COMPACT) {
-      ++ri;
-      row = __ldg(nz_id + ri);
-      row_end = __ldg(nz_end + ri);
-      x = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row * K + l * 4));
-      return;
-    }
-    int e, probes = 0;
-    do {
-      ++row;
-      e = __ldg(row_ptr + row + 1);
-    } while (e <= next_entry && ++probes < 16);
-    if (e <= next_entry) {
-      int lo = row + 1, hi = M + 1;
-      while (lo < hi) {
-        const int mid = (lo + hi) >> 1;
-        if (__ldg(row_ptr + mid) <= next_entry)
-          lo = mid + 1;
-        else
-          hi = mid;
-      }
-      row = lo - 1;
-      e = __ldg(row_ptr + row + 1);
-    }
-    row_end = e;
+    (void)next_entry;   // the list of rows that hold entries names the row directly
+    ++ri;
+    row = __ldg(nz_id + ri);
+    row_end = __ldg(nz_end + ri);
     x = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row * K + l * 4));
   };
 
@@ -252,15 +231,11 @@ void launch_sddmm(bool hint, int M, int n_chunks, const int32_t* row_ptr, const 
   constexpr int BT = 64;
   const int cpb = BT / 32;
   const unsigned grid = (unsigned)((n_chunks + cpb - 1) / cpb);
-#define HPSPMM_SDDMM_LAUNCH(H, CP)                                                                        \
-  sddmm_warp_kernel<W, H, BT, SLAB, CP><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,      \
-                                                            chunk_start, chunk_row, chunk_order, ld,      \
-                                                            rows.nz_id, rows.nz_end, rows.chunk_ri)
-  if (rows.nz_id != nullptr) {
-    if (hint) HPSPMM_SDDMM_LAUNCH(true, true); else HPSPMM_SDDMM_LAUNCH(false, true);
-  } else {
-    if (hint) HPSPMM_SDDMM_LAUNCH(true, false); else HPSPMM_SDDMM_LAUNCH(false, false);
-  }
+#define HPSPMM_SDDMM_LAUNCH(H)                                                                            \
+  sddmm_warp_kernel<W, H, BT, SLAB><<<grid, BT, 0, s>>>(M, n_chunks, row_ptr, col_idx, X, Y, out,          \
+                                                        chunk_start, chunk_row, chunk_order, ld,          \
+                                                        rows.nz_id, rows.nz_end, rows.chunk_ri)
+  if (hint) HPSPMM_SDDMM_LAUNCH(true); else HPSPMM_SDDMM_LAUNCH(false);
 #undef HPSPMM_SDDMM_LAUNCH
 }
 

@@ -100,8 +100,17 @@ __device__ __forceinline__ void advance_row(const int* __restrict__ row_ptr, int
   int probes = 0;
   while (e == j) {
     if (++probes == 8) {
-      // a long run of empty rows: finish with a binary search for the row holding j
-      int lo = row + 1, hi = M + 1;
+      // a long run of empty rows: gallop (8, 16, 32, ... rows ahead) to bracket the row holding j,
+      // then a binary search inside the bracket
+      int lo = row + 1, step = 8, hi;
+      for (;;) {
+        hi = min(lo + step, M);
+        if (hi == M || __ldg(row_ptr + hi) > j) break;
+        lo = hi;
+        step <<= 1;
+      }
+      ++hi;
+      ++lo;
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
         if (__ldg(row_ptr + mid) <= j)
@@ -420,8 +429,17 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
       e = __ldg(row_ptr + row + 1);
     } while (e == next_entry && ++probes < 16);
     if (e == next_entry) {
-      // a long run of empty rows: binary search for the row that holds next_entry
-      int lo = row + 1, hi = M + 1;
+      // a long run of empty rows: gallop (16, 32, 64, ... rows ahead) to bracket the row that holds
+      // next_entry, then a binary search inside the bracket
+      int lo = row + 1, step = 16, hi;
+      for (;;) {
+        hi = min(lo + step, M);
+        if (hi == M || __ldg(row_ptr + hi) > next_entry) break;
+        lo = hi;
+        step <<= 1;
+      }
+      ++hi;
+      ++lo;
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
         if (__ldg(row_ptr + mid) <= next_entry)
