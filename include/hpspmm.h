@@ -135,8 +135,9 @@ HPSPMM_API int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int
                                    const int32_t* col_idx, const float* vals, const float* B,
                                    float* C, const hpspmm_opts* opts, hpspmm_stream stream);
 
-/* Chunk table of A for repeated products with the same sparsity structure (a GNN
- * reuses it across layers and epochs).  Reads row_ptr on the device, synchronises
+/* Chunk table of A, the order in which chunks are scheduled, and the list of rows that
+ * hold entries, for repeated products with the same sparsity structure (a GNN reuses
+ * them across layers and epochs).  Reads row_ptr on the device, synchronises
  * the stream once.  col_idx may be NULL (N is then ignored); when given, the pieces
  * of rows longer than a chunk are scheduled in ascending order of the column band
  * they read, which raises the L2 hit rate of the gathers by a few per cent.  The
