@@ -98,6 +98,7 @@ PROTOTYPES = {
                                      POINTER(Opts), _P]),
     "hpspmm_csr_transpose": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P]),
     "hpspmm_plan_tables": (c_int, [_P, POINTER(_P), POINTER(_P), POINTER(_P)]),
+    "hpspmm_plan_row_list": (c_int, [_P, POINTER(_P), POINTER(_P), POINTER(_P)]),
     "hpspmm_layer_create": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _I64, _P, POINTER(_P)]),
     "hpspmm_layer_destroy": (c_int, [_P, _P]),
     "hpspmm_layer_info": (c_int, [_P, POINTER(_I64), POINTER(_I64), POINTER(_I64), POINTER(_I64),
@@ -293,6 +294,12 @@ class Context:
         """Device addresses of chunk_start, chunk_row, chunk_order."""
         a, b, c = _P(), _P(), _P()
         self._check(self.lib.hpspmm_plan_tables(plan, byref(a), byref(b), byref(c)), "hpspmm_plan_tables")
+        return a.value, b.value, c.value
+
+    def plan_row_list(self, plan):
+        """Device addresses of nz_id, nz_end, chunk_ri."""
+        a, b, c = _P(), _P(), _P()
+        self._check(self.lib.hpspmm_plan_row_list(plan, byref(a), byref(b), byref(c)), "hpspmm_plan_row_list")
         return a.value, b.value, c.value
 
     def spmm_csr(self, M, N, K, nnz, row_ptr, col_idx, vals, B, C, plan=None, opts=None, stream=None):

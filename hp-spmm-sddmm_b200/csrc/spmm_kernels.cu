@@ -1399,6 +1399,15 @@ int hpspmm_plan_tables(const hpspmm_plan* plan, const int32_t** chunk_start, con
   return HPSPMM_OK;
 }
 
+int hpspmm_plan_row_list(const hpspmm_plan* plan, const int32_t** nz_id, const int32_t** nz_end,
+                         const int32_t** chunk_ri) {
+  if (!plan) return HPSPMM_ERR_INVALID;
+  if (nz_id) *nz_id = plan->nz_id;
+  if (nz_end) *nz_end = plan->nz_end;
+  if (chunk_ri) *chunk_ri = plan->chunk_ri;
+  return HPSPMM_OK;
+}
+
 int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int64_t N, int64_t K,
                         int64_t nnz, const int32_t* row_ptr, const int32_t* col_idx,
                         const float* vals, const float* B, float* C, const hpspmm_opts* opts,

@@ -158,6 +158,12 @@ HPSPMM_API int hpspmm_plan_info(const hpspmm_plan* plan, int64_t* n_chunks,
  * (the chunk ids in the order in which warps take them: a permutation of 0..n_chunks-1). */
 HPSPMM_API int hpspmm_plan_tables(const hpspmm_plan* plan, const int32_t** chunk_start,
                                   const int32_t** chunk_row, const int32_t** chunk_order);
+/* Device pointers to the plan's list of rows that hold entries, for inspection: nz_id (row
+ * ids, ascending, followed by the sentinel M), nz_end (row_ptr[id + 1] of those rows; the
+ * sentinel's is INT32_MAX), chunk_ri[n_chunks] (position in the list of the row that holds
+ * a chunk's first entry).  The kernels step through this list and never visit an empty row. */
+HPSPMM_API int hpspmm_plan_row_list(const hpspmm_plan* plan, const int32_t** nz_id,
+                                    const int32_t** nz_end, const int32_t** chunk_ri);
 
 /* The same product for callers that cannot allocate device memory when they need it.
  * (No counterpart in the reference, whose entry points allocate nothing because its

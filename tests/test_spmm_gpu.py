@@ -211,6 +211,14 @@ def test_plan_tables_tile_the_matrix_and_schedule_every_chunk_once(gpu_ctx, pkg,
     nonempty = np.diff(start) > 0
     assert np.all(rp[row[nonempty]] <= start[:-1][nonempty]) and np.all(start[:-1][nonempty] < rp[row[nonempty] + 1])
     assert np.array_equal(np.sort(order), np.arange(n, dtype=np.int32))
+    # the list of rows that hold entries: exactly those rows, in order, with their ends and a sentinel
+    p_id, p_end, p_ri = ctx.plan_row_list(plan)
+    want_id = np.flatnonzero(np.diff(rp) > 0).astype(np.int32)
+    n_nz = len(want_id)
+    got_id, got_end, ri = read(p_id, n_nz + 1), read(p_end, n_nz + 1), read(p_ri, n)
+    assert np.array_equal(got_id[:n_nz], want_id) and got_id[n_nz] == M
+    assert np.array_equal(got_end[:n_nz], rp[want_id + 1]) and got_end[n_nz] == np.iinfo(np.int32).max
+    assert np.array_equal(got_id[ri], row)
     ctx.plan_destroy(plan)
     d_rp.free()
     d_ci.free()
