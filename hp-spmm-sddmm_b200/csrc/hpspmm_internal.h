@@ -94,8 +94,8 @@ struct hpspmm_device_guard {
 int hpspmm_ensure_scratch(hpspmm_ctx* ctx, size_t bytes);
 int hpspmm_ensure_stage(hpspmm_ctx* ctx, size_t bytes);
 
-// nominal chunk size for a dense width
-int32_t hpspmm_default_chunk_nnz(int64_t K);
+// nominal chunk size for a dense width and a matrix of nnz entries
+int32_t hpspmm_default_chunk_nnz(int64_t K, int64_t nnz);
 
 // Builds chunk_start / chunk_row for (M, nnz, row_ptr) into the given arrays (device).
 // split_count (device int, may be null) receives the number of chunks ending mid-row.

@@ -277,7 +277,7 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
     n_chunks = plan->n_chunks;
     rows = sddmm_row_list{plan->nz_id, plan->nz_end, plan->chunk_ri};
   } else {
-    int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
+    int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K, nnz);
     S = (S + 31) / 32 * 32;
     n_chunks = (nnz + S - 1) / S;
     const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);

@@ -1151,12 +1151,27 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace
 
-int32_t hpspmm_default_chunk_nnz(int64_t K) {
-  // measured on B200 (R-MAT scale 20, cost-ordered chunks): the best nominal chunk grows with
-  // the row width -- 128 entries at K = 32, 160 at K = 64, 256 at K = 128
+// Nominal chunk size of the kernels that probe row_ptr or reduce into C (the allocation-free entry, the COO
+// product): measured best on B200 (R-MAT scale 20) at 128 / 160 / 256 entries for K = 32 / 64 / 128.
+static int32_t probing_chunk_nnz(int64_t K) {
   if (K <= 32) return 128;
   if (K <= 64) return 160;
   return 256;
+}
+
+int32_t hpspmm_default_chunk_nnz(int64_t K, int64_t nnz) {
+  // With the list of non-empty rows a row end costs two loads, and larger chunks amortise the per-chunk
+  // prologue (table loads, pipeline fill) and leave fewer carries.  Measured on B200 (R-MAT scale 20, product
+  // time in ms at S = 128 / 256 / 320 / 512 / 1024): K = 32: 0.240 / 0.217 / 0.208 / 0.199 / 0.193;
+  // K = 64: 0.356 / 0.314 / 0.307 / 0.310 / 0.306; K = 128: 0.630 / 0.563 / 0.563 / 0.595 / 0.592.
+  // Small matrices keep smaller chunks so that there are still several waves of them
+  // (148 SMs x 40 resident warps x 4).
+  const int32_t floor_s = probing_chunk_nnz(K);
+  const int32_t best = K <= 32 ? 512 : (K <= 64 ? 320 : 256);
+  const int64_t want = nnz / 24000 / 32 * 32;
+  int64_t s = want < floor_s ? floor_s : want;
+  if (s > best) s = best;
+  return (int32_t)s;
 }
 
 int hpspmm_launch_chunk_table(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int32_t* row_ptr,
@@ -1302,7 +1317,7 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0 && max_K >= 1, "bad size");
   HPSPMM_REQUIRE(ctx, row_ptr != nullptr, "null row_ptr");
   if (M > 2147483646ll || nnz > 2147483647ll - 4096) return HPSPMM_ERR_UNSUPPORTED;
-  int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(max_K);
+  int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(max_K, nnz);
   S = (S + 31) / 32 * 32;
   hpspmm_device_guard guard(ctx->device);
   hpspmm_plan* p = new (std::nothrow) hpspmm_plan();
@@ -1434,7 +1449,7 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
                     plan->chunk_order, plan->n_split_chunks > 0, s, plan->chunk_nnz, plan->run_counter,
                     row_list{plan->nz_id, plan->nz_end, plan->chunk_ri});
   }
-  int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
+  int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K, nnz);
   S = (S + 31) / 32 * 32;
   const int64_t n_chunks = (nnz + S - 1) / S;
   const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
@@ -1498,7 +1513,7 @@ static int host_product_slabs(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, 
   if (st != HPSPMM_OK) return st;
   // size the kernel scratch before anything is queued (growing it synchronises the device)
   {
-    const int32_t S = (opts && opts->chunk_nnz > 0) ? (opts->chunk_nnz + 31) / 32 * 32 : hpspmm_default_chunk_nnz(KS);
+    const int32_t S = (opts && opts->chunk_nnz > 0) ? (opts->chunk_nnz + 31) / 32 * 32 : hpspmm_default_chunk_nnz(KS, nnz);
     const int64_t n_chunks = (nnz + S - 1) / S;
     const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
     const size_t b_sort = hpspmm_order_scratch_bytes(n_chunks), b_list = hpspmm_row_list_scratch_bytes(M);
@@ -1630,7 +1645,7 @@ int hpspmm_spmm_coo_f32(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_
   if (K % 32 == 0 && K <= 512) {
     // 32/64/128 directly, other multiples of 32 as column slabs of 128, 64 and 32 (every slab accumulates into
     // its own columns of C, so the slabs are independent)
-    int32_t Sw = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K);
+    int32_t Sw = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : probing_chunk_nnz(K);
     Sw = (Sw + 31) / 32 * 32;
     constexpr int BT = 64;
     const int64_t n_w = (nnz_padded + Sw - 1) / Sw;
@@ -1728,7 +1743,7 @@ extern "C" int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M,
   }
   if (M == 0) return HPSPMM_OK;
 
-  const int32_t S = hpspmm_default_chunk_nnz(K);
+  const int32_t S = probing_chunk_nnz(K);
   const int64_t n_chunks = (nnz + S - 1) / S;
   const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
   const size_t b_cval = align_up((size_t)(n_chunks + 1) * (size_t)K * 4, 256);

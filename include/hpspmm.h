@@ -186,7 +186,9 @@ HPSPMM_API int hpspmm_plan_row_list(const hpspmm_plan* plan, const int32_t** nz_
  * overlap on the GPU (different streams, or different host threads) race on it, so
  * serialise them.  Nothing has to be cleared between calls: each call rewrites everything
  * it later reads.  Pointers are device pointers on device_ordinal; results equal those of
- * hpspmm_spmm_csr_f32 with default options bit for bit.  err_buf may be NULL. */
+ * hpspmm_spmm_csr_f32 within the parity tolerance, and bit for bit whenever both use the
+ * same nominal chunk size (K > 64, or matrices of fewer than about 4 M entries).
+ * err_buf may be NULL. */
 HPSPMM_API int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M, int64_t N,
                                                   int64_t K, int64_t nnz, const int32_t* row_ptr,
                                                   const int32_t* col_idx, const float* vals,
