@@ -39,8 +39,8 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the K = 128 product kernel on
 # the N = 1 workload, from the ncu capture summarised in profiles/spmm_warp_kernel_rmat20.md
-# (1314.3 MB read + 522.3 MB written; the same full-size workload, about 1 GB on the device).
-NCU_TRAFFIC_BYTES_K128 = 1836592200
+# (1314.4 MB read + 522.1 MB written; the same full-size workload, about 1 GB on the device).
+NCU_TRAFFIC_BYTES_K128 = 1836496216
 
 
 def load_peak():
