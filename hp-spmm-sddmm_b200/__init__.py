@@ -34,6 +34,10 @@ ALGO_AUTO = 0
 ALGO_BALANCED = 1
 ALGO_ROW_SPLIT = 2
 
+EXCHANGE_NEEDED_ROWS = 0
+EXCHANGE_ALL_ROWS = 1
+COMM_ID_BYTES = 128
+
 VALS_ONES = 0
 VALS_U01 = 1
 VALS_UPM1 = 2
@@ -131,6 +135,19 @@ PROTOTYPES = {
     "hpspmm_row_length_cv": (c_double, [_I64, _P]),
     "hpspmm_spmm_algorithmic_bytes": (c_double, [_I64, _I64, _I64, _I64]),
     "hpspmm_sddmm_algorithmic_bytes": (c_double, [_I64, _I64, _I64, _I64, _I64]),
+    "hpspmm_shard_needed_rows": (c_int, [_I64, _P, _I64, c_int32, _P, _P, _P, _P, POINTER(_I64)]),
+    "hpspmm_comm_unique_id": (c_int, [_P]),
+    "hpspmm_comm_create": (c_int, [_P, c_int32, c_int32, _P, POINTER(_P)]),
+    "hpspmm_comm_destroy": (c_int, [_P]),
+    "hpspmm_comm_info": (c_int, [_P, POINTER(c_int32), POINTER(c_int32)]),
+    "hpspmm_shard_plan_create": (c_int, [_P, _P, _I64, _I64, _I64, _P, _P, _P, _I64, c_int32, _P, POINTER(_P)]),
+    "hpspmm_shard_plan_destroy": (c_int, [_P, _P]),
+    "hpspmm_shard_plan_info": (c_int, [_P, POINTER(_I64), POINTER(_I64), POINTER(_I64), POINTER(_I64)]),
+    "hpspmm_sharded_exchange_begin": (c_int, [_P, _P, c_int32, _I64, _P, _P]),
+    "hpspmm_sharded_product": (c_int, [_P, _P, c_int32, _I64, _P, _P, POINTER(Opts), _P]),
+    "hpspmm_spmm_sharded_f32": (c_int, [_P, _P, _I64, _P, _P, _P, POINTER(Opts), _P]),
+    "hpspmm_probe_gather_gbs": (c_int, [_P, c_int32, _I64, _I64, c_int32, _I64, c_double, c_int32,
+                                        POINTER(c_double), POINTER(c_double)]),
 }
 
 _lib = None
@@ -375,6 +392,14 @@ class Context:
     def launch_count(self):
         return self.lib.hpspmm_ctx_launch_count(self.handle)
 
+    def probe_gather(self, row_bytes, table_rows, n_gathers, pattern=1, hot_rows=0, hot_share=0.0, repeats=10):
+        """GB/s and ms per launch of the bare gather shape (hpspmm_probe_gather_gbs)."""
+        gbs, ms = c_double(), c_double()
+        self._check(self.lib.hpspmm_probe_gather_gbs(self.handle, row_bytes, table_rows, n_gathers, pattern,
+                                                     hot_rows, hot_share, repeats, byref(gbs), byref(ms)),
+                    "hpspmm_probe_gather_gbs")
+        return gbs.value, ms.value
+
 
 # ---- host side ---------------------------------------------------------------------------
 
@@ -509,6 +534,86 @@ def shard_csr(row_ptr, col_idx, vals, row_lo, row_hi):
     _gen_check(lib, lib.hpspmm_shard_row_ptr(row_ptr.ctypes.data, row_lo, row_hi, local.ctypes.data,
                                              byref(lo), byref(n)), "hpspmm_shard_row_ptr")
     return local, col_idx[lo.value:lo.value + n.value], vals[lo.value:lo.value + n.value]
+
+
+def shard_needed_rows(col_idx, N, b_bounds):
+    """Rows of B a shard references: (col_compact, need_rows, need_off) of hpspmm_shard_needed_rows."""
+    lib = load_library()
+    col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+    b_bounds = np.ascontiguousarray(b_bounds, dtype=np.int64)
+    world = len(b_bounds) - 1
+    nnz = len(col_idx)
+    col_compact = np.empty(nnz, dtype=np.int32)
+    need = np.empty(max(1, min(int(N), max(nnz, 1))), dtype=np.int32)
+    off = np.empty(world + 1, dtype=np.int64)
+    n = _I64()
+    _gen_check(lib, lib.hpspmm_shard_needed_rows(nnz, col_idx.ctypes.data, N, world, b_bounds.ctypes.data,
+                                                 col_compact.ctypes.data, need.ctypes.data, off.ctypes.data,
+                                                 byref(n)), "hpspmm_shard_needed_rows")
+    return col_compact, need[:n.value].copy(), off
+
+
+def comm_unique_id():
+    """128 bytes that identify a new communicator; create on one rank, carry to the others."""
+    lib = load_library()
+    buf = (ctypes.c_ubyte * COMM_ID_BYTES)()
+    _gen_check(lib, lib.hpspmm_comm_unique_id(buf), "hpspmm_comm_unique_id")
+    return bytes(buf)
+
+
+class ShardedSpmm:
+    """One rank's side of the row-sharded product (hpspmm_comm_* / hpspmm_shard_plan_* / hpspmm_sharded_*).
+
+    row_ptr / col_idx are the shard's HOST arrays (global column ids); b_bounds says which rank owns
+    which rows of B.  comm_id: bytes from comm_unique_id() of one rank (None when world == 1)."""
+
+    def __init__(self, ctx, world, rank, comm_id, M_local, N, row_ptr, col_idx, b_bounds, max_K,
+                 exchange=EXCHANGE_NEEDED_ROWS, stream=None):
+        self.ctx, self.world, self.rank = ctx, world, rank
+        self.comm, self.plan = _P(), _P()
+        idbuf = (ctypes.c_ubyte * COMM_ID_BYTES).from_buffer_copy(comm_id) if comm_id is not None else None
+        ctx._check(ctx.lib.hpspmm_comm_create(ctx.handle, world, rank, idbuf, byref(self.comm)), "hpspmm_comm_create")
+        self._row_ptr = np.ascontiguousarray(row_ptr, dtype=np.int32)
+        self._col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+        self._bounds = np.ascontiguousarray(b_bounds, dtype=np.int64)
+        self.M_local, self.N, self.nnz_local = int(M_local), int(N), len(self._col_idx)
+        self.rows_own = int(self._bounds[rank + 1] - self._bounds[rank])
+        try:
+            ctx._check(ctx.lib.hpspmm_shard_plan_create(ctx.handle, self.comm, self.M_local, self.N, self.nnz_local,
+                                                        self._row_ptr.ctypes.data, self._col_idx.ctypes.data,
+                                                        self._bounds.ctypes.data, max_K, exchange, stream,
+                                                        byref(self.plan)), "hpspmm_shard_plan_create")
+        except Exception:
+            ctx.lib.hpspmm_comm_destroy(self.comm)
+            self.comm = _P()
+            raise
+
+    def info(self):
+        v = [_I64() for _ in range(4)]
+        self.ctx._check(self.ctx.lib.hpspmm_shard_plan_info(self.plan, *[byref(x) for x in v]), "hpspmm_shard_plan_info")
+        return dict(zip(("rows_local", "rows_received", "rows_sent", "device_bytes"), (x.value for x in v)))
+
+    def begin(self, slot, K, B_own, stream=None):
+        self.ctx._check(self.ctx.lib.hpspmm_sharded_exchange_begin(self.ctx.handle, self.plan, slot, K, _ptr(B_own),
+                                                                   stream), "hpspmm_sharded_exchange_begin")
+
+    def product(self, slot, K, vals, C_local, opts=None, stream=None):
+        self.ctx._check(self.ctx.lib.hpspmm_sharded_product(self.ctx.handle, self.plan, slot, K, _ptr(vals),
+                                                            _ptr(C_local), byref(opts) if opts else None, stream),
+                        "hpspmm_sharded_product")
+
+    def spmm(self, K, vals, B_own, C_local, opts=None, stream=None):
+        self.ctx._check(self.ctx.lib.hpspmm_spmm_sharded_f32(self.ctx.handle, self.plan, K, _ptr(vals), _ptr(B_own),
+                                                             _ptr(C_local), byref(opts) if opts else None, stream),
+                        "hpspmm_spmm_sharded_f32")
+
+    def close(self):
+        if self.plan:
+            self.ctx.lib.hpspmm_shard_plan_destroy(self.ctx.handle, self.plan)
+            self.plan = _P()
+        if self.comm:
+            self.ctx.lib.hpspmm_comm_destroy(self.comm)
+            self.comm = _P()
 
 
 def gflops(nnz, K, ms):

@@ -25,6 +25,8 @@ SOURCES = [
     "sddmm_kernels.cu",
     "structure_kernels.cu",
     "graph_layer.cu",
+    "probe_kernels.cu",
+    "sharded_product.cu",
     "host_side.cpp",
 ]
 
@@ -79,7 +81,7 @@ def build(force=False, verbose=False, ptxas_info=False):
     if ptxas_info:
         for _, out in results:
             print(out)
-    _run([nvcc] + ARCH + ["-shared", "-o", LIB_PATH] + objs + ["-Xcompiler", "-fopenmp", "-lgomp"],
+    _run([nvcc] + ARCH + ["-shared", "-o", LIB_PATH] + objs + ["-Xcompiler", "-fopenmp", "-lgomp", "-ldl"],
          verbose)
     return LIB_PATH
 

@@ -378,6 +378,41 @@ int hpspmm_shard_row_ptr(const int32_t* row_ptr_host, int64_t row_lo, int64_t ro
   return HPSPMM_OK;
 }
 
+int hpspmm_shard_needed_rows(int64_t nnz_local, const int32_t* col_idx_host, int64_t N, int32_t world,
+                             const int64_t* b_bounds, int32_t* col_compact_out, int32_t* need_rows_out,
+                             int64_t* need_off_out, int64_t* n_needed_out) {
+  if (nnz_local < 0 || N < 1 || N > 2147483646ll || world < 1 || !b_bounds || !need_off_out || !n_needed_out)
+    return HPSPMM_ERR_INVALID;
+  if (nnz_local > 0 && (!col_idx_host || !col_compact_out || !need_rows_out)) return HPSPMM_ERR_INVALID;
+  if (b_bounds[0] != 0 || b_bounds[world] != N) return HPSPMM_ERR_INVALID;
+  for (int32_t s = 0; s < world; ++s)
+    if (b_bounds[s] > b_bounds[s + 1]) return HPSPMM_ERR_INVALID;
+  // mark, number (an exclusive scan over the marks), renumber
+  std::vector<int32_t> id((size_t)N + 1, 0);
+  int bad = 0;
+#pragma omp parallel for schedule(static) reduction(| : bad)
+  for (int64_t j = 0; j < nnz_local; ++j) {
+    const int32_t c = col_idx_host[j];
+    if (c < 0 || c >= N)
+      bad |= 1;
+    else
+      id[(size_t)c] = 1;   // benign race: every writer stores the same value
+  }
+  if (bad) return HPSPMM_ERR_BAD_CSR;
+  int32_t run = 0;
+  for (int64_t c = 0; c < N; ++c) {
+    const int32_t m = id[(size_t)c];
+    id[(size_t)c] = run;
+    if (m) need_rows_out[run++] = (int32_t)c;
+  }
+  id[(size_t)N] = run;
+  for (int32_t s = 0; s <= world; ++s) need_off_out[s] = id[(size_t)b_bounds[s]];
+#pragma omp parallel for schedule(static)
+  for (int64_t j = 0; j < nnz_local; ++j) col_compact_out[j] = id[(size_t)col_idx_host[j]];
+  *n_needed_out = run;
+  return HPSPMM_OK;
+}
+
 double hpspmm_gflops(int64_t nnz, int64_t K, double ms) {
   return (double)nnz * (double)K * 2.0 / ms / 1.0e6;
 }

@@ -1226,7 +1226,10 @@ int run_slab(hpspmm_ctx* ctx, bool hint, int m, int nc, const int32_t* row_ptr, 
   const bool settle = run_counter != nullptr && W >= 16;
   // strided slabs carry two more live values (the stride) and spill at 48 registers: 16 blocks per SM
   // (64 registers) took the K = 256 product from 1.44 to 1.20 ms
-  constexpr int MINB = STRIDED ? 16 : 20;
+#ifndef HPSPMM_WARP_MINB
+#define HPSPMM_WARP_MINB 20
+#endif
+  constexpr int MINB = STRIDED ? 16 : HPSPMM_WARP_MINB;
   int st = launch_warp<W, 4, MINB, 64, STRIDED>(ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start,
                                                 chunk_row, carry_row, carry_val, chunk_order, S,
                                                 settle ? run_counter : nullptr, stream, ld, rows);

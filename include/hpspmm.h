@@ -374,6 +374,70 @@ HPSPMM_API int hpspmm_shard_row_ptr(const int32_t* row_ptr_host, int64_t row_lo,
                                     int32_t* local_row_ptr, int64_t* nnz_lo_out,
                                     int64_t* nnz_local_out);
 
+/* Which rows of B a shard references, and the shard's columns renumbered into that list.
+ * col_idx_host[nnz_local] holds global column ids in [0, N); rank s owns rows
+ * [b_bounds[s], b_bounds[s+1]) of B (world + 1 ascending bounds from 0 to N).  Outputs:
+ * need_rows_out (capacity min(N, nnz_local)): the distinct columns, ascending, i.e. owner after
+ * owner; need_off_out[world + 1]: where every owner's part starts in that list;
+ * col_compact_out[nnz_local]: position of col_idx_host[j] in the list; *n_needed_out its length.
+ * Integer outputs, deterministic.  No counterpart in the reference (single GPU). */
+HPSPMM_API int hpspmm_shard_needed_rows(int64_t nnz_local, const int32_t* col_idx_host, int64_t N,
+                                        int32_t world, const int64_t* b_bounds,
+                                        int32_t* col_compact_out, int32_t* need_rows_out,
+                                        int64_t* need_off_out, int64_t* n_needed_out);
+
+/* ---- multi-GPU: row-sharded product, rows of B exchanged over NCCL -------------------------------
+ * One process per GPU.  Rank r holds rows [bounds[r], bounds[r+1]) of A and of C (hpspmm_shard_bounds)
+ * and the rows [b_bounds[r], b_bounds[r+1]) of B (for a square graph the same bounds: a vertex's
+ * features live where its row of A lives).  C stays row-sharded.  The reference is single-GPU
+ * (test/test_all.cpp:27-109); nothing below has a counterpart there.
+ *
+ * comm: a communicator over NCCL (looked up at run time with dlopen; NCCL is needed only when
+ *   world > 1).  hpspmm_comm_unique_id on one rank, its 128 bytes carried to the others by any
+ *   means the host program has, then hpspmm_comm_create on every rank (collective).
+ * shard plan (collective, synchronises): from the shard's HOST row_ptr / col_idx it lists the rows
+ *   of B the shard references per owner (HPSPMM_EXCHANGE_NEEDED_ROWS) or takes all of them
+ *   (HPSPMM_EXCHANGE_ALL_ROWS, the plain all-gather), renumbers the shard's columns into that list,
+ *   tells every owner which rows to send, and keeps device copies of row_ptr and the renumbered
+ *   columns.  Every rank must pass the same b_bounds, max_K and exchange mode.
+ * exchange_begin: enqueues, on the plan's own stream and after what `stream` holds now, the packing
+ *   of the rows the other ranks need and one grouped NCCL send / receive; remote rows land in this
+ *   GPU's own memory.  product: waits (stream event) for that slot's rows, then runs the local
+ *   product on `stream`.  Slots 0..3 are independent buffers: begin several products, then multiply
+ *   them in turn, and each exchange overlaps the previous product.  All ranks must issue their begins
+ *   in the same order.  The first use of a slot (or a wider K on it) allocates and synchronises.
+ * hpspmm_spmm_sharded_f32 = exchange_begin + product on slot 0.
+ * vals: the shard's values (device, nnz_local); B_own: rows_own x K (device); C_local: M_local x K.
+ * No kernel reads another GPU's memory and nothing waits on the device: ordering is by stream events. */
+typedef struct hpspmm_comm hpspmm_comm;
+typedef struct hpspmm_shard_plan hpspmm_shard_plan;
+enum { HPSPMM_COMM_ID_BYTES = 128 };
+enum { HPSPMM_EXCHANGE_NEEDED_ROWS = 0, HPSPMM_EXCHANGE_ALL_ROWS = 1 };
+HPSPMM_API int hpspmm_comm_unique_id(unsigned char* id_out);
+HPSPMM_API int hpspmm_comm_create(hpspmm_ctx* ctx, int32_t world, int32_t rank,
+                                  const unsigned char* id, hpspmm_comm** out);
+HPSPMM_API int hpspmm_comm_destroy(hpspmm_comm* comm);
+HPSPMM_API int hpspmm_comm_info(const hpspmm_comm* comm, int32_t* world, int32_t* rank);
+HPSPMM_API int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local,
+                                        int64_t N, int64_t nnz_local, const int32_t* row_ptr_host,
+                                        const int32_t* col_idx_host, const int64_t* b_bounds,
+                                        int64_t max_K, int32_t exchange, hpspmm_stream stream,
+                                        hpspmm_shard_plan** out);
+HPSPMM_API int hpspmm_shard_plan_destroy(hpspmm_ctx* ctx, hpspmm_shard_plan* plan);
+/* rows of the local dense operand (own + received), rows received from and sent to other ranks
+ * per product, device bytes the plan holds */
+HPSPMM_API int hpspmm_shard_plan_info(const hpspmm_shard_plan* plan, int64_t* rows_local,
+                                      int64_t* rows_received, int64_t* rows_sent,
+                                      int64_t* device_bytes);
+HPSPMM_API int hpspmm_sharded_exchange_begin(hpspmm_ctx* ctx, hpspmm_shard_plan* plan, int32_t slot,
+                                             int64_t K, const float* B_own, hpspmm_stream stream);
+HPSPMM_API int hpspmm_sharded_product(hpspmm_ctx* ctx, hpspmm_shard_plan* plan, int32_t slot,
+                                      int64_t K, const float* vals, float* C_local,
+                                      const hpspmm_opts* opts, hpspmm_stream stream);
+HPSPMM_API int hpspmm_spmm_sharded_f32(hpspmm_ctx* ctx, hpspmm_shard_plan* plan, int64_t K,
+                                       const float* vals, const float* B_own, float* C_local,
+                                       const hpspmm_opts* opts, hpspmm_stream stream);
+
 /* ---- host side: metric -----------------------------------------------------------------------------
  * GFLOPS = 2*nnz*K / ms / 1e6 with the unpadded nnz (spmm/mm/spmm_common.cpp:24-31);
  * row-length coefficient of variation (spmm/mm/spmm_common.cpp:57-67, :349-374). */
@@ -383,6 +447,21 @@ HPSPMM_API double hpspmm_row_length_cv(int64_t M, const int32_t* row_ptr_host);
 HPSPMM_API double hpspmm_spmm_algorithmic_bytes(int64_t M, int64_t N_ref, int64_t K, int64_t nnz);
 HPSPMM_API double hpspmm_sddmm_algorithmic_bytes(int64_t M_ref, int64_t N_ref, int64_t K,
                                                  int64_t M, int64_t nnz);
+
+/* ---- diagnostics: load-path ceilings ---------------------------------------------------------------
+ * Times the gather shape of the product kernels alone (lane groups of row_bytes / 16 lanes,
+ * one 16-byte load per lane, four gathers in flight per lane, no sparse stream, no stores):
+ * n_gathers rows of row_bytes (128, 256 or 512) bytes from a zero-filled table of table_rows rows
+ * that the call allocates and frees.  pattern 0 walks the table row after row (a stream), 1 picks
+ * rows uniformly at random, 2 does the same but sends a share hot_share of the gathers to the first
+ * hot_rows rows.  A table smaller than the L2 cache gives the L2 -> SM ceiling, a larger one the
+ * DRAM-backed gather rate.  Returns GB/s (and ms per launch) averaged over `repeats` launches after
+ * three warm-up launches; synchronises.  The reference has no counterpart (its README reports
+ * kernel GFLOPS only); the number bounds what any gather-based product can reach on the GPU. */
+HPSPMM_API int hpspmm_probe_gather_gbs(hpspmm_ctx* ctx, int32_t row_bytes, int64_t table_rows,
+                                       int64_t n_gathers, int32_t pattern, int64_t hot_rows,
+                                       double hot_share, int32_t repeats, double* gbs_out,
+                                       double* ms_out);
 
 #ifdef __cplusplus
 }
