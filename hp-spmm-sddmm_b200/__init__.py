@@ -36,6 +36,7 @@ ALGO_ROW_SPLIT = 2
 
 EXCHANGE_NEEDED_ROWS = 0
 EXCHANGE_ALL_ROWS = 1
+EXCHANGE_NEEDED_ROWS_NCCL = 2
 COMM_ID_BYTES = 128
 
 VALS_ONES = 0
@@ -97,10 +98,13 @@ PROTOTYPES = {
                                                    ctypes.c_char_p, c_size_t]),
     "hpspmm_spmm_csr_f32_host": (c_int, [_P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P,
                                          POINTER(Opts)]),
+    "hpspmm_spmm_csr_f32_host_multi": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, c_int32, _P, _P, _P,
+                                               POINTER(Opts)]),
     "hpspmm_spmm_coo_f32": (c_int, [_P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, POINTER(Opts), _P]),
     "hpspmm_sddmm_csr_f32": (c_int, [_P, _P, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P,
                                      POINTER(Opts), _P]),
     "hpspmm_csr_transpose": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "hpspmm_spmm_kernel_signature": (c_int, [_P, _I64, c_int32, ctypes.c_char_p, c_size_t]),
     "hpspmm_plan_tables": (c_int, [_P, POINTER(_P), POINTER(_P), POINTER(_P)]),
     "hpspmm_plan_row_list": (c_int, [_P, POINTER(_P), POINTER(_P), POINTER(_P)]),
     "hpspmm_layer_create": (c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _I64, _P, POINTER(_P)]),
@@ -146,6 +150,7 @@ PROTOTYPES = {
     "hpspmm_sharded_exchange_begin": (c_int, [_P, _P, c_int32, _I64, _P, _P]),
     "hpspmm_sharded_product": (c_int, [_P, _P, c_int32, _I64, _P, _P, POINTER(Opts), _P]),
     "hpspmm_spmm_sharded_f32": (c_int, [_P, _P, _I64, _P, _P, _P, POINTER(Opts), _P]),
+    "hpspmm_debug_fail_device_alloc": (c_int, [_I64]),
     "hpspmm_probe_gather_gbs": (c_int, [_P, c_int32, _I64, _I64, c_int32, _I64, c_double, c_int32,
                                         POINTER(c_double), POINTER(c_double)]),
 }
@@ -307,6 +312,11 @@ class Context:
         return {"n_chunks": a.value, "n_split_chunks": b.value, "chunk_nnz": c.value,
                 "scratch_bytes": d.value}
 
+    def kernel_signature(self, plan, K, b_l2_hint=0):
+        buf = ctypes.create_string_buffer(256)
+        self._check(self.lib.hpspmm_spmm_kernel_signature(plan, K, b_l2_hint, buf, 256), "hpspmm_spmm_kernel_signature")
+        return buf.value.decode()
+
     def plan_tables(self, plan):
         """Device addresses of chunk_start, chunk_row, chunk_order."""
         a, b, c = _P(), _P(), _P()
@@ -330,6 +340,17 @@ class Context:
                                                       _ptr(col_idx), _ptr(vals), _ptr(B), _ptr(C),
                                                       byref(opts) if opts else None),
                     "hpspmm_spmm_csr_f32_host")
+
+    def spmm_csr_host_multi(self, M, N, nnz, row_ptr, col_idx, vals, Ks, Bs, Cs, opts=None):
+        """C_i = A * B_i for host arrays (or raw host addresses) B_i, C_i; A is uploaded once."""
+        n = len(Ks)
+        ks = (_I64 * n)(*[int(k) for k in Ks])
+        bs = (_P * n)(*[_ptr(b) for b in Bs])
+        cs = (_P * n)(*[_ptr(c) for c in Cs])
+        self._check(self.lib.hpspmm_spmm_csr_f32_host_multi(self.handle, M, N, nnz, _ptr(row_ptr), _ptr(col_idx),
+                                                            _ptr(vals), n, ks, bs, cs,
+                                                            byref(opts) if opts else None),
+                    "hpspmm_spmm_csr_f32_host_multi")
 
     def spmm_coo(self, M, N, K, nnz_padded, row_idx, col_idx, vals, B, C, opts=None, stream=None):
         self._check(self.lib.hpspmm_spmm_coo_f32(self.handle, M, N, K, nnz_padded, _ptr(row_idx),

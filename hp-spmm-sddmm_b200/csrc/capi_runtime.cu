@@ -2,11 +2,36 @@
 // Stands where the reference has starml::Matrix, its allocators, handles and copy
 // operators (include/starml/basic/matrix.h:14-77, spmm/starml/basic/allocator_cuda.cpp:5-24,
 // spmm/starml/basic/handle_cuda.cpp:4-23, spmm/starml/operators/cuda/copy_kernel.cu:7-41).
+#include <atomic>
 #include <new>
 
 #include "hpspmm_internal.h"
 
+// Allocation-failure seam for tests: > 0 counts down with every device allocation, the one that
+// reaches zero fails; 0 = disarmed.
+static std::atomic<int64_t> g_fail_alloc_countdown{0};
+
+cudaError_t hpspmm_device_malloc(void** out, size_t bytes) {
+  int64_t left = g_fail_alloc_countdown.load(std::memory_order_relaxed);
+  while (left > 0) {
+    if (g_fail_alloc_countdown.compare_exchange_weak(left, left - 1, std::memory_order_relaxed)) {
+      if (left == 1) {
+        if (out) *out = nullptr;
+        return cudaErrorMemoryAllocation;
+      }
+      break;
+    }
+  }
+  return cudaMalloc(out, bytes);
+}
+
 extern "C" {
+
+int hpspmm_debug_fail_device_alloc(int64_t nth) {
+  if (nth < 0) return HPSPMM_ERR_INVALID;
+  g_fail_alloc_countdown.store(nth, std::memory_order_relaxed);
+  return HPSPMM_OK;
+}
 
 const char* hpspmm_status_string(int status) {
   switch (status) {
@@ -42,7 +67,7 @@ int hpspmm_ctx_create(int device_ordinal, hpspmm_ctx** out) {
   ctx->l2_bytes = v;
   cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, device_ordinal);
   ctx->max_smem_optin = v;
-  e = cudaMalloc((void**)&ctx->flag, 256);
+  e = hpspmm_device_malloc((void**)&ctx->flag, 256);
   if (e != cudaSuccess) {
     delete ctx;
     return e == cudaErrorMemoryAllocation ? HPSPMM_ERR_OOM : HPSPMM_ERR_CUDA;
@@ -61,6 +86,8 @@ int hpspmm_ctx_destroy(hpspmm_ctx* ctx) {
   if (ctx->flag) cudaFree(ctx->flag);
   for (int i = 0; i < 3; ++i)
     if (ctx->pipe_streams[i]) cudaStreamDestroy(ctx->pipe_streams[i]);
+  for (int i = 0; i < 8; ++i)
+    if (ctx->pipe_events[i]) cudaEventDestroy(ctx->pipe_events[i]);
   delete ctx;
   return HPSPMM_OK;
 }
@@ -76,7 +103,7 @@ int hpspmm_dev_alloc(hpspmm_ctx* ctx, size_t bytes, void** out) {
   *out = nullptr;
   if (bytes == 0) return HPSPMM_OK;
   hpspmm_device_guard guard(ctx->device);
-  HPSPMM_CUDA_TRY(ctx, cudaMalloc(out, bytes));
+  HPSPMM_CUDA_TRY(ctx, hpspmm_device_malloc(out, bytes));
   return HPSPMM_OK;
 }
 
@@ -208,10 +235,10 @@ int hpspmm_ensure_scratch(hpspmm_ctx* ctx, size_t bytes) {
   ctx->scratch = nullptr;
   ctx->scratch_bytes = 0;
   size_t want = bytes + bytes / 4 + 4096;
-  cudaError_t e = cudaMalloc(&ctx->scratch, want);
+  cudaError_t e = hpspmm_device_malloc(&ctx->scratch, want);
   if (e != cudaSuccess) {
     want = bytes;
-    e = cudaMalloc(&ctx->scratch, want);
+    e = hpspmm_device_malloc(&ctx->scratch, want);
   }
   if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_OOM, "scratch cudaMalloc", e);
   ctx->scratch_bytes = want;
@@ -224,7 +251,7 @@ int hpspmm_ensure_stage(hpspmm_ctx* ctx, size_t bytes) {
   if (ctx->stage) cudaFree(ctx->stage);
   ctx->stage = nullptr;
   ctx->stage_bytes = 0;
-  cudaError_t e = cudaMalloc(&ctx->stage, bytes);
+  cudaError_t e = hpspmm_device_malloc(&ctx->stage, bytes);
   if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_OOM, "stage cudaMalloc", e);
   ctx->stage_bytes = bytes;
   return HPSPMM_OK;

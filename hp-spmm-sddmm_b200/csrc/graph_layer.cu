@@ -97,10 +97,10 @@ int hpspmm_layer_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, cons
   g->col_idx = col_idx;
   g->vals = vals;
   const size_t b_rp = (size_t)(N + 1) * 4, b_e = (size_t)(nnz > 0 ? nnz : 1) * 4;
-  cudaError_t e = cudaMalloc((void**)&g->row_ptr_t, b_rp);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&g->col_idx_t, b_e);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&g->vals_t, b_e);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&g->perm, b_e);
+  cudaError_t e = hpspmm_device_malloc((void**)&g->row_ptr_t, b_rp);
+  if (e == cudaSuccess) e = hpspmm_device_malloc((void**)&g->col_idx_t, b_e);
+  if (e == cudaSuccess) e = hpspmm_device_malloc((void**)&g->vals_t, b_e);
+  if (e == cudaSuccess) e = hpspmm_device_malloc((void**)&g->perm, b_e);
   if (e != cudaSuccess) {
     release(ctx, g);
     return hpspmm_set_err(ctx, HPSPMM_ERR_OOM, "layer cudaMalloc", e);

@@ -25,6 +25,7 @@ struct hpspmm_ctx {
   int* flag;  // one device int used by validation and plan building
   // streams of the host-buffer entry point: uploads, kernels, downloads (created on first use)
   cudaStream_t pipe_streams[3];
+  cudaEvent_t pipe_events[8];   // "A has landed" and, per buffer, slab uploaded / multiplied / downloaded
   char err[256];
 };
 
@@ -90,6 +91,15 @@ struct hpspmm_device_guard {
     if (switched) cudaSetDevice(prev);
   }
 };
+
+// Every device allocation of the library goes through here: cudaMalloc, unless a test has armed
+// hpspmm_debug_fail_device_alloc, in which case the chosen allocation reports cudaErrorMemoryAllocation
+// without touching the device.
+cudaError_t hpspmm_device_malloc(void** out, size_t bytes);
+template <typename T>
+static inline cudaError_t hpspmm_device_malloc(T** out, size_t bytes) {
+  return hpspmm_device_malloc(reinterpret_cast<void**>(out), bytes);
+}
 
 int hpspmm_ensure_scratch(hpspmm_ctx* ctx, size_t bytes);
 int hpspmm_ensure_stage(hpspmm_ctx* ctx, size_t bytes);

@@ -84,8 +84,8 @@ extern "C" int hpspmm_probe_gather_gbs(hpspmm_ctx* ctx, int32_t row_bytes, int64
   float* sink = nullptr;
   cudaEvent_t a = nullptr, b = nullptr;
   const size_t table_bytes = (size_t)table_rows * (size_t)row_bytes;
-  cudaError_t e = cudaMalloc((void**)&table, table_bytes);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&sink, (size_t)warps * 4);
+  cudaError_t e = hpspmm_device_malloc((void**)&table, table_bytes);
+  if (e == cudaSuccess) e = hpspmm_device_malloc((void**)&sink, (size_t)warps * 4);
   if (e == cudaSuccess) e = cudaMemset(table, 0, table_bytes);
   if (e == cudaSuccess) e = cudaEventCreate(&a);
   if (e == cudaSuccess) e = cudaEventCreate(&b);

@@ -122,14 +122,25 @@ sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
 
   float4 x = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row * K + l * 4));
   const float* Yl = Y + l * 4;
+  // The fragment of the NEXT row of X that holds entries is fetched one row ahead: a row of X is a miss to L2
+  // or DRAM, and fetched on demand its latency would be paid once per row (every 15 entries on a power-law
+  // graph's short rows) with nothing of the same warp to overlap it.  The list ends in the sentinel row M,
+  // which has no fragment.
+  int row_n = __ldg(nz_id + ri + 1);
+  int row_end_n = __ldg(nz_end + ri + 1);
+  float4 xn = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (row_n < M) xn = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row_n * K + l * 4));
 
-  // entry `next_entry` starts a later row: find it and fetch its fragment of X
+  // entry `next_entry` starts a later row: step to it and start fetching the one after
   auto next_x = [&](int next_entry) {
     (void)next_entry;   // the list of rows that hold entries names the row directly
     ++ri;
-    row = __ldg(nz_id + ri);
-    row_end = __ldg(nz_end + ri);
-    x = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row * K + l * 4));
+    row = row_n;
+    row_end = row_end_n;
+    x = xn;
+    row_n = __ldg(nz_id + ri + 1);
+    row_end_n = __ldg(nz_end + ri + 1);
+    if (row_n < M) xn = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row_n * K + l * 4));
   };
 
   int stage = 0;

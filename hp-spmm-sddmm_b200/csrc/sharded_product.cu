@@ -17,10 +17,23 @@
 // layers of a model that are evaluated together, or the K = 32 / 64 / 128 products of the benchmark) begins
 // them all and then multiplies them in turn: while one slot multiplies, the next slot's rows are in flight.
 //
+// Transport.  By default the rows are PUSHED: one kernel per exchange reads the rows the other ranks need
+// from B_own and stores them straight into the receivers' dense operands through peer mappings of those
+// buffers (CUDA IPC, plain stores over NVLink / NVSwitch, every SM taking part), the own referenced rows
+// going to the local operand by the same launch; no send buffer, no second copy.  A four-byte NCCL
+// all-reduce behind the kernel is the completion signal: when it has finished on a rank, every rank's push
+// kernel has, and a kernel's stores are visible once it has ended.  Every slot holds two operand buffers used
+// in turn, and a rank joins a slot's next signal only after its own last product on that slot has read its
+// buffer, so a push never overtakes the product that still reads its target.  With
+// HPSPMM_EXCHANGE_NEEDED_ROWS_NCCL (or when a peer mapping cannot be had) the rows are packed into a send
+// buffer and travel by grouped ncclSend / ncclRecv instead; measured on two B200s that path moves 0.36 TB/s
+// per direction, the push 0.6 TB/s or more.  No TMA and no multicast anywhere in this file.
+//
 // NCCL is looked up at run time (dlopen of libnccl.so.2; the copy a host framework has already loaded is
 // reused), so the library itself links against nothing but the CUDA runtime and single-GPU users need no
-// NCCL at all.  No kernel of this file reads another GPU's memory: remote rows always land in local HBM
-// first, and there is no device-side wait anywhere (stream events only).
+// NCCL at all.  No kernel of this file READS another GPU's memory (each row of B is gathered many times, so
+// remote rows always land in local HBM first), and there is no device-side wait anywhere: ordering is by
+// stream events and by the completion of NCCL operations.
 #include <dlfcn.h>
 
 #include <algorithm>
@@ -39,6 +52,9 @@ struct nccl_id {
 typedef void* nccl_comm_t;
 constexpr int kNcclInt32 = 2;    // ncclInt32
 constexpr int kNcclFloat32 = 7;  // ncclFloat32
+constexpr int kNcclUint8 = 1;    // ncclUint8
+constexpr int kNcclSum = 0;      // ncclSum
+constexpr int kMaxPushWorld = 16;
 
 struct nccl_api {
   void* handle;
@@ -48,6 +64,7 @@ struct nccl_api {
   int (*Send)(const void*, size_t, int, int, nccl_comm_t, cudaStream_t);
   int (*Recv)(void*, size_t, int, int, nccl_comm_t, cudaStream_t);
   int (*AllGather)(const void*, void*, size_t, int, nccl_comm_t, cudaStream_t);
+  int (*AllReduce)(const void*, void*, size_t, int, int, nccl_comm_t, cudaStream_t);
   int (*GroupStart)();
   int (*GroupEnd)();
   const char* (*GetErrorString)(int);
@@ -82,6 +99,7 @@ const nccl_api* load_nccl(char* err, size_t err_len) {
   HPSPMM_BIND(Send, "ncclSend")
   HPSPMM_BIND(Recv, "ncclRecv")
   HPSPMM_BIND(AllGather, "ncclAllGather")
+  HPSPMM_BIND(AllReduce, "ncclAllReduce")
   HPSPMM_BIND(GroupStart, "ncclGroupStart")
   HPSPMM_BIND(GroupEnd, "ncclGroupEnd")
   HPSPMM_BIND(GetErrorString, "ncclGetErrorString")
@@ -99,6 +117,38 @@ __global__ void rebase_rows_kernel(int* __restrict__ rows, int64_t n, int base) 
 
 constexpr int kSlots = 4;
 
+// Where the rows of one exchange go: destination after destination in the order of the send list
+// (the other ranks ascending, then this rank itself).
+struct push_targets {
+  float* base[kMaxPushWorld];      // receiver's dense operand (a peer mapping, or the local buffer)
+  int64_t first_row[kMaxPushWorld];   // row of that operand where this rank's block starts
+  int64_t list_begin[kMaxPushWorld + 1];   // positions in the send list
+  int n;
+};
+
+// dst_d[first_row_d + i - list_begin_d, :] = B_own[send_rows[i], :] for every position i of the send list;
+// one 16-byte (VEC = 4) or 4-byte element per thread step, rows written whole and in order, so the
+// stores that cross NVLink are contiguous runs of K * 4 bytes.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+push_rows_kernel(const float* __restrict__ B_own, const int* __restrict__ send_rows, int64_t total_rows,
+                 int64_t row_elems, push_targets t) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t total = total_rows * row_elems;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const int64_t i = e / row_elems, c = e - i * row_elems;
+    int d = 0;
+#pragma unroll 1
+    while (d + 1 < t.n && i >= t.list_begin[d + 1]) ++d;
+    const int64_t src = (int64_t)__ldg(send_rows + i) * row_elems + c;
+    const int64_t dst = (t.first_row[d] + (i - t.list_begin[d])) * row_elems + c;
+    if (VEC == 4)
+      reinterpret_cast<float4*>(t.base[d])[dst] = __ldg(reinterpret_cast<const float4*>(B_own) + src);
+    else
+      t.base[d][dst] = __ldg(B_own + src);
+  }
+}
+
 }  // namespace
 
 struct hpspmm_comm {
@@ -110,8 +160,11 @@ struct hpspmm_comm {
 
 struct hpspmm_shard_slot {
   int64_t K_cap;        // width the buffers and the plan were sized for (0 = unused)
-  float* send_buf;      // rows for the other ranks, destination after destination
-  float* B_local;       // the n_needed x K matrix the product reads
+  float* send_buf;      // NCCL transport: rows for the other ranks, destination after destination
+  float* B_local[2];    // the n_needed x K matrix the product reads; push transport: two, used in turn
+  float* peer[2][kMaxPushWorld];   // push transport: the other ranks' B_local buffers, mapped here
+  int phase;            // which of the two buffers the last begin filled
+  bool begun;           // an exchange has been begun and its product not yet enqueued
   hpspmm_plan* plan;    // chunk table of the shard for this width class
   cudaEvent_t ev_in, ev_landed, ev_read;
   bool read_pending;    // a product of this slot has been enqueued since the last begin
@@ -132,6 +185,9 @@ struct hpspmm_shard_plan {
   int32_t* d_col;                    // shard's columns renumbered into B_local's rows
   int32_t* d_send_rows;              // local row ids of B_own, grouped as send_off says
   cudaStream_t comm_stream;
+  bool push;                         // rows travel by peer stores (else by NCCL send / receive)
+  std::vector<int64_t> dst_first_row;   // world: where this rank's block starts in rank d's dense operand
+  int32_t* d_token;                  // four bytes for the completion signal
   hpspmm_shard_slot slots[kSlots];
   size_t device_bytes;
 };
@@ -152,32 +208,88 @@ int nccl_fail(hpspmm_ctx* ctx, const nccl_api* api, const char* what, int rc) {
 // position of destination d in the send order (others ascending, self last)
 inline int send_slot_of(int d, int rank, int world) { return d == rank ? world - 1 : (d < rank ? d : d - 1); }
 
+void release_slot_buffers(hpspmm_ctx* ctx, hpspmm_shard_plan* p, hpspmm_shard_slot& s) {
+  for (int b = 0; b < 2; ++b) {
+    for (int d = 0; d < kMaxPushWorld; ++d)
+      if (s.peer[b][d]) {
+        cudaIpcCloseMemHandle(s.peer[b][d]);
+        s.peer[b][d] = nullptr;
+      }
+    if (s.B_local[b]) cudaFree(s.B_local[b]);
+    s.B_local[b] = nullptr;
+  }
+  if (s.send_buf) cudaFree(s.send_buf);
+  s.send_buf = nullptr;
+  if (s.plan) hpspmm_plan_destroy(ctx, s.plan);
+  s.plan = nullptr;
+  s.K_cap = 0;
+  (void)p;
+}
+
+// First use of a slot at this width (or a wider one): allocate the operand buffers, build the chunk table and,
+// for the push transport, map every other rank's buffers.  Collective when world > 1; synchronises.
 int ensure_slot(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int slot, int64_t K, cudaStream_t user_stream) {
   hpspmm_shard_slot& s = p->slots[slot];
   if (s.K_cap >= K && s.plan != nullptr) return HPSPMM_OK;
-  // first use of the slot at this width (or a wider one): allocate, build the chunk table.  Synchronises.
   HPSPMM_CUDA_TRY(ctx, cudaDeviceSynchronize());
-  if (s.send_buf) cudaFree(s.send_buf);
-  if (s.B_local) cudaFree(s.B_local);
-  if (s.plan) hpspmm_plan_destroy(ctx, s.plan);
-  s.send_buf = s.B_local = nullptr;
-  s.plan = nullptr;
-  s.K_cap = 0;
-  const size_t b_send = align_up((size_t)std::max<int64_t>(p->send_remote, 1) * (size_t)K * 4, 256);
+  release_slot_buffers(ctx, p, s);
+  const int world = p->world, rank = p->rank;
+  const int n_buf = p->push ? 2 : 1;
   const size_t b_loc = align_up((size_t)std::max<int64_t>(p->n_needed, 1) * (size_t)K * 4, 256);
-  HPSPMM_CUDA_TRY(ctx, cudaMalloc((void**)&s.send_buf, b_send));
-  HPSPMM_CUDA_TRY(ctx, cudaMalloc((void**)&s.B_local, b_loc));
-  p->device_bytes += b_send + b_loc;
+  for (int b = 0; b < n_buf; ++b) {
+    HPSPMM_CUDA_TRY(ctx, hpspmm_device_malloc((void**)&s.B_local[b], b_loc));
+    p->device_bytes += b_loc;
+  }
+  if (!p->push) {
+    const size_t b_send = align_up((size_t)std::max<int64_t>(p->send_remote, 1) * (size_t)K * 4, 256);
+    HPSPMM_CUDA_TRY(ctx, hpspmm_device_malloc((void**)&s.send_buf, b_send));
+    p->device_bytes += b_send;
+  }
   if (!s.ev_in) {
     HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.ev_in, cudaEventDisableTiming));
     HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.ev_landed, cudaEventDisableTiming));
     HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.ev_read, cudaEventDisableTiming));
+  }
+  if (p->push && world > 1) {
+    // every rank publishes the handles of its two buffers; all ranks map all of them
+    const nccl_api* api = p->comm->api;
+    const size_t hb = sizeof(cudaIpcMemHandle_t);
+    std::vector<unsigned char> mine(2 * hb), all((size_t)world * 2 * hb);
+    for (int b = 0; b < 2; ++b) {
+      cudaIpcMemHandle_t h;
+      HPSPMM_CUDA_TRY(ctx, cudaIpcGetMemHandle(&h, s.B_local[b]));
+      memcpy(mine.data() + b * hb, &h, hb);
+    }
+    unsigned char* d_h = nullptr;
+    HPSPMM_CUDA_TRY(ctx, hpspmm_device_malloc((void**)&d_h, (size_t)(world + 1) * 2 * hb));
+    cudaError_t e = cudaMemcpyAsync(d_h, mine.data(), 2 * hb, cudaMemcpyHostToDevice, user_stream);
+    int rc = 0;
+    if (e == cudaSuccess) rc = api->AllGather(d_h, d_h + 2 * hb, 2 * hb, kNcclUint8, p->comm->comm, user_stream);
+    if (e == cudaSuccess && rc == 0)
+      e = cudaMemcpyAsync(all.data(), d_h + 2 * hb, (size_t)world * 2 * hb, cudaMemcpyDeviceToHost, user_stream);
+    if (e == cudaSuccess && rc == 0) e = cudaStreamSynchronize(user_stream);
+    cudaFree(d_h);
+    if (rc != 0) return nccl_fail(ctx, api, "ncclAllGather(buffer handles)", rc);
+    if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "buffer handle exchange", e);
+    for (int d = 0; d < world; ++d) {
+      if (d == rank) continue;
+      for (int b = 0; b < 2; ++b) {
+        cudaIpcMemHandle_t h;
+        memcpy(&h, all.data() + ((size_t)d * 2 + b) * hb, hb);
+        void* ptr = nullptr;
+        e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "cudaIpcOpenMemHandle(peer operand)", e);
+        s.peer[b][d] = (float*)ptr;
+      }
+    }
   }
   int st = hpspmm_plan_create(ctx, p->M_local, p->n_needed, p->nnz_local, p->d_row_ptr, p->d_col, K, nullptr,
                               (hpspmm_stream)user_stream, &s.plan);
   if (st != HPSPMM_OK) return st;
   s.K_cap = K;
   s.read_pending = false;
+  s.begun = false;
+  s.phase = 0;
   return HPSPMM_OK;
 }
 
@@ -256,7 +368,8 @@ int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local
   HPSPMM_REQUIRE(ctx, M_local >= 0 && N >= 1 && nnz_local >= 0 && max_K >= 1, "bad size");
   HPSPMM_REQUIRE(ctx, row_ptr_host != nullptr && (nnz_local == 0 || col_idx_host != nullptr) && b_bounds != nullptr,
                  "null array");
-  HPSPMM_REQUIRE(ctx, exchange == HPSPMM_EXCHANGE_NEEDED_ROWS || exchange == HPSPMM_EXCHANGE_ALL_ROWS,
+  HPSPMM_REQUIRE(ctx, exchange == HPSPMM_EXCHANGE_NEEDED_ROWS || exchange == HPSPMM_EXCHANGE_ALL_ROWS ||
+                          exchange == HPSPMM_EXCHANGE_NEEDED_ROWS_NCCL,
                  "unknown exchange mode");
   if (N > 2147483646ll || nnz_local > 2147483647ll - 4096) return HPSPMM_ERR_UNSUPPORTED;
   const int world = comm->world, rank = comm->rank;
@@ -278,6 +391,8 @@ int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local
   p->max_K = max_K;
   p->rows_own = b_bounds[rank + 1] - b_bounds[rank];
   p->d_row_ptr = p->d_col = p->d_send_rows = nullptr;
+  p->d_token = nullptr;
+  p->push = exchange == HPSPMM_EXCHANGE_NEEDED_ROWS && world <= kMaxPushWorld;
   p->comm_stream = nullptr;
   p->device_bytes = 0;
   memset(p->slots, 0, sizeof(p->slots));
@@ -287,7 +402,8 @@ int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local
   std::vector<int32_t> need_rows;
   std::vector<int64_t> need_off((size_t)world + 1);
   int st = HPSPMM_OK;
-  if (exchange == HPSPMM_EXCHANGE_NEEDED_ROWS) {
+  const bool needed_only = exchange != HPSPMM_EXCHANGE_ALL_ROWS;
+  if (needed_only) {
     need_rows.resize((size_t)std::min<int64_t>(N, std::max<int64_t>(nnz_local, 1)));
     st = hpspmm_shard_needed_rows(nnz_local, col_idx_host, N, world, b_bounds, col_compact.data(), need_rows.data(),
                                   need_off.data(), &p->n_needed);
@@ -314,7 +430,7 @@ int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local
   if (cudaStreamCreateWithFlags(&p->comm_stream, cudaStreamNonBlocking) != cudaSuccess)
     PLAN_FAIL(hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "comm stream", cudaGetLastError()));
   if (world > 1) {
-    e = cudaMalloc((void**)&d_cnt, (size_t)(world + 1) * world * 4);
+    e = hpspmm_device_malloc((void**)&d_cnt, (size_t)(world + 1) * world * 4);
     if (e != cudaSuccess) PLAN_FAIL(hpspmm_set_err(ctx, HPSPMM_ERR_OOM, "plan cudaMalloc", e));
     e = cudaMemcpyAsync(d_cnt, want.data(), (size_t)world * 4, cudaMemcpyHostToDevice, us);
     if (e == cudaSuccess) {
@@ -337,6 +453,10 @@ int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local
   }
   p->send_remote = p->send_off[world - 1];
   const int64_t send_total = p->send_off[world];
+  // where this rank's block starts in rank d's dense operand: d wants all_want[d][s] rows from every s < rank first
+  p->dst_first_row.assign((size_t)world, 0);
+  for (int d = 0; d < world; ++d)
+    for (int s2 = 0; s2 < rank; ++s2) p->dst_first_row[d] += all_want[(size_t)d * world + s2];
   for (int d = 0; d < world; ++d)
     if (p->send_cnt[d] > p->rows_own) {
       snprintf(ctx->err, sizeof(ctx->err), "rank %d asks for more rows than this rank owns", d);
@@ -349,19 +469,22 @@ int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local
   const size_t b_send = align_up((size_t)std::max<int64_t>(send_total, 1) * 4, 256);
   const size_t b_need = align_up((size_t)std::max<int64_t>(p->n_needed, 1) * 4, 256);
   char* base = nullptr;
-  e = cudaMalloc((void**)&base, b_rp + b_col + b_send + b_need);
+  e = hpspmm_device_malloc((void**)&base, b_rp + b_col + b_send + b_need + 256);
   if (e != cudaSuccess) PLAN_FAIL(hpspmm_set_err(ctx, HPSPMM_ERR_OOM, "plan cudaMalloc", e));
   p->device_bytes += b_rp + b_col + b_send + b_need;
   p->d_row_ptr = (int32_t*)base;
   p->d_col = (int32_t*)(base + b_rp);
   p->d_send_rows = (int32_t*)(base + b_rp + b_col);
   int32_t* d_need = (int32_t*)(base + b_rp + b_col + b_send);   // only used while the lists are exchanged
+  p->d_token = (int32_t*)(base + b_rp + b_col + b_send + b_need);
+  if (cudaMemsetAsync(p->d_token, 0, 256, us) != cudaSuccess)
+    PLAN_FAIL(hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "plan memset", cudaGetLastError()));
   e = cudaMemcpyAsync(p->d_row_ptr, row_ptr_host, (size_t)(M_local + 1) * 4, cudaMemcpyHostToDevice, us);
   if (e == cudaSuccess && nnz_local > 0)
     e = cudaMemcpyAsync(p->d_col, col_compact.data(), (size_t)nnz_local * 4, cudaMemcpyHostToDevice, us);
   if (e != cudaSuccess) PLAN_FAIL(hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "plan upload", e));
 
-  if (exchange == HPSPMM_EXCHANGE_NEEDED_ROWS) {
+  if (needed_only) {
     // every owner receives the global ids of the rows wanted from it and makes them local
     if (p->n_needed > 0)
       e = cudaMemcpyAsync(d_need, need_rows.data(), (size_t)p->n_needed * 4, cudaMemcpyHostToDevice, us);
@@ -393,7 +516,7 @@ int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local
   e = cudaStreamSynchronize(us);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) PLAN_FAIL(hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "shard plan build", e));
-  if (exchange == HPSPMM_EXCHANGE_NEEDED_ROWS && send_total > 0) {
+  if (needed_only && send_total > 0) {
     // a malformed request (a row outside this rank's block) must not turn into a wild gather
     std::vector<int32_t> chk((size_t)send_total);
     e = cudaMemcpy(chk.data(), p->d_send_rows, (size_t)send_total * 4, cudaMemcpyDeviceToHost);
@@ -416,9 +539,7 @@ int hpspmm_shard_plan_destroy(hpspmm_ctx* ctx, hpspmm_shard_plan* p) {
   cudaDeviceSynchronize();
   for (int i = 0; i < kSlots; ++i) {
     hpspmm_shard_slot& s = p->slots[i];
-    if (s.send_buf) cudaFree(s.send_buf);
-    if (s.B_local) cudaFree(s.B_local);
-    if (s.plan) hpspmm_plan_destroy(ctx, s.plan);
+    release_slot_buffers(ctx, p, s);
     if (s.ev_in) cudaEventDestroy(s.ev_in);
     if (s.ev_landed) cudaEventDestroy(s.ev_landed);
     if (s.ev_read) cudaEventDestroy(s.ev_read);
@@ -453,14 +574,54 @@ int hpspmm_sharded_exchange_begin(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int32_t
   if (st != HPSPMM_OK) return st;
   hpspmm_shard_slot& s = p->slots[slot];
   const int world = p->world, rank = p->rank;
+  HPSPMM_REQUIRE(ctx, !s.begun, "the slot was begun again before its product was enqueued");
   // the exchange starts once B_own is ready and the last product of this slot has read its buffer
   HPSPMM_CUDA_TRY(ctx, cudaEventRecord(s.ev_in, us));
   HPSPMM_CUDA_TRY(ctx, cudaStreamWaitEvent(cs, s.ev_in, 0));
   if (s.read_pending) HPSPMM_CUDA_TRY(ctx, cudaStreamWaitEvent(cs, s.ev_read, 0));
   s.read_pending = false;
   const int self = send_slot_of(rank, rank, world);
-  float* own_dst = s.B_local + p->recv_off[rank] * K;
-  if (p->exchange == HPSPMM_EXCHANGE_NEEDED_ROWS) {
+  if (p->push) {
+    // one kernel stores every referenced row where it will be read: the other ranks' operands through their
+    // peer mappings, this rank's own rows into its own operand
+    s.phase ^= 1;
+    const int b = s.phase;
+    const int64_t total_rows = p->send_off[world];
+    if (total_rows > 0) {
+      push_targets t;
+      memset(&t, 0, sizeof(t));
+      t.n = world;
+      for (int d = 0; d < world; ++d) {
+        const int pos = send_slot_of(d, rank, world);
+        t.base[pos] = d == rank ? s.B_local[b] : s.peer[b][d];
+        t.first_row[pos] = p->dst_first_row[d];
+        t.list_begin[pos] = p->send_off[pos];
+      }
+      t.list_begin[world] = total_rows;
+      const bool vec = (K & 3) == 0;
+      const int64_t row_elems = vec ? K / 4 : K;
+      int64_t blocks = (total_rows * row_elems + 255) / 256;
+      const int64_t cap = (int64_t)ctx->sm_count * 16;
+      if (blocks > cap) blocks = cap;
+      if (vec)
+        push_rows_kernel<4><<<(unsigned)blocks, 256, 0, cs>>>(B_own, p->d_send_rows, total_rows, row_elems, t);
+      else
+        push_rows_kernel<1><<<(unsigned)blocks, 256, 0, cs>>>(B_own, p->d_send_rows, total_rows, row_elems, t);
+      ctx->launches++;
+      HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
+    }
+    if (world > 1) {
+      // completion signal: finished here = every rank's push kernel has ended
+      const nccl_api* api = p->comm->api;
+      HPSPMM_NCCL_TRY(ctx, api, api->AllReduce(p->d_token, p->d_token + 1, 1, kNcclInt32, kNcclSum, p->comm->comm, cs));
+    }
+    HPSPMM_CUDA_TRY(ctx, cudaEventRecord(s.ev_landed, cs));
+    s.begun = true;
+    return HPSPMM_OK;
+  }
+  float* Bl = s.B_local[0];
+  float* own_dst = Bl + p->recv_off[rank] * K;
+  if (p->exchange != HPSPMM_EXCHANGE_ALL_ROWS) {
     // rows for the others -> send buffer; own referenced rows -> straight into their place
     if (p->send_remote > 0) {
       st = hpspmm_gather_rows_f32(ctx, p->send_remote, K, B_own, p->d_send_rows, s.send_buf, (hpspmm_stream)cs);
@@ -480,7 +641,7 @@ int hpspmm_sharded_exchange_begin(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int32_t
     for (int d = 0; d < world && rc == 0; ++d) {
       if (d == rank) continue;
       const int64_t n_recv = p->recv_off[d + 1] - p->recv_off[d];
-      if (p->exchange == HPSPMM_EXCHANGE_NEEDED_ROWS) {
+      if (p->exchange != HPSPMM_EXCHANGE_ALL_ROWS) {
         if (p->send_cnt[d] > 0)
           rc = api->Send(s.send_buf + p->send_off[send_slot_of(d, rank, world)] * K, (size_t)(p->send_cnt[d] * K),
                          kNcclFloat32, d, p->comm->comm, cs);
@@ -488,12 +649,13 @@ int hpspmm_sharded_exchange_begin(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int32_t
         rc = api->Send(B_own, (size_t)(p->rows_own * K), kNcclFloat32, d, p->comm->comm, cs);
       }
       if (rc == 0 && n_recv > 0)
-        rc = api->Recv(s.B_local + p->recv_off[d] * K, (size_t)(n_recv * K), kNcclFloat32, d, p->comm->comm, cs);
+        rc = api->Recv(Bl + p->recv_off[d] * K, (size_t)(n_recv * K), kNcclFloat32, d, p->comm->comm, cs);
     }
     const int rc2 = api->GroupEnd();
     if (rc != 0 || rc2 != 0) return nccl_fail(ctx, api, "row exchange", rc != 0 ? rc : rc2);
   }
   HPSPMM_CUDA_TRY(ctx, cudaEventRecord(s.ev_landed, cs));
+  s.begun = true;
   return HPSPMM_OK;
 }
 
@@ -507,10 +669,11 @@ int hpspmm_sharded_product(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int32_t slot, 
   cudaStream_t us = (cudaStream_t)stream;
   HPSPMM_CUDA_TRY(ctx, cudaStreamWaitEvent(us, s.ev_landed, 0));
   int st = hpspmm_spmm_csr_f32(ctx, s.plan, p->M_local, p->n_needed, K, p->nnz_local, p->d_row_ptr, p->d_col, vals,
-                               s.B_local, C_local, opts, stream);
+                               s.B_local[p->push ? s.phase : 0], C_local, opts, stream);
   if (st != HPSPMM_OK) return st;
   HPSPMM_CUDA_TRY(ctx, cudaEventRecord(s.ev_read, us));
   s.read_pending = true;
+  s.begun = false;
   return HPSPMM_OK;
 }
 

@@ -30,6 +30,11 @@ using namespace hpspmm;
 
 constexpr int kBlockThreads = 256;
 
+// resident 64-thread blocks per SM the contiguous warp kernels are compiled for (20 -> 48 registers)
+#ifndef HPSPMM_WARP_MINB
+#define HPSPMM_WARP_MINB 20
+#endif
+
 // ---- chunk table -----------------------------------------------------------------------
 
 __global__ void chunk_table_kernel(int M, int nnz, const int* __restrict__ row_ptr, int S,
@@ -1226,9 +1231,6 @@ int run_slab(hpspmm_ctx* ctx, bool hint, int m, int nc, const int32_t* row_ptr, 
   const bool settle = run_counter != nullptr && W >= 16;
   // strided slabs carry two more live values (the stride) and spill at 48 registers: 16 blocks per SM
   // (64 registers) took the K = 256 product from 1.44 to 1.20 ms
-#ifndef HPSPMM_WARP_MINB
-#define HPSPMM_WARP_MINB 20
-#endif
   constexpr int MINB = STRIDED ? 16 : HPSPMM_WARP_MINB;
   int st = launch_warp<W, 4, MINB, 64, STRIDED>(ctx, hint, m, nc, row_ptr, col_idx, vals, B, C, chunk_start,
                                                 chunk_row, carry_row, carry_val, chunk_order, S,
@@ -1343,7 +1345,7 @@ int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const
   const size_t b_sort = hpspmm_order_scratch_bytes(p->n_chunks);   // only needed while building
   p->bytes = b_start + b_row + b_crow + b_cval + b_order + b_count + 2 * b_nz + b_ri + b_sort;
   char* base = nullptr;
-  cudaError_t e = cudaMalloc((void**)&base, p->bytes);
+  cudaError_t e = hpspmm_device_malloc((void**)&base, p->bytes);
   if (e != cudaSuccess) {
     delete p;
     return hpspmm_set_err(ctx, HPSPMM_ERR_OOM, "plan cudaMalloc", e);
@@ -1405,6 +1407,22 @@ int hpspmm_plan_info(const hpspmm_plan* plan, int64_t* n_chunks, int64_t* n_spli
   if (n_split_chunks) *n_split_chunks = plan->n_split_chunks;
   if (chunk_nnz) *chunk_nnz = plan->chunk_nnz;
   if (scratch_bytes) *scratch_bytes = (int64_t)plan->bytes;
+  return HPSPMM_OK;
+}
+
+int hpspmm_spmm_kernel_signature(const hpspmm_plan* plan, int64_t K, int32_t b_l2_hint, char* buf, size_t len) {
+  if (!buf || len == 0 || K < 1) return HPSPMM_ERR_INVALID;
+  const bool hint = b_l2_hint == 2 || (b_l2_hint == 0 && K >= 64);
+  if (K == 32 || K == 64 || K == 128) {
+    const int W = (int)K / 4;
+    // the template arguments of spmm_warp_kernel as run_slab / launch_warp choose them
+    snprintf(buf, len, "spmm_warp_kernel<%d,4,%d,%d,64,%d,0,1> chunk_nnz=%d", W, HPSPMM_WARP_MINB, hint ? 1 : 0,
+             W >= 16 ? 1 : 0, plan ? (int)plan->chunk_nnz : (int)hpspmm_default_chunk_nnz(K, plan ? plan->nnz : 0));
+  } else if (K % 32 == 0 && K <= 512) {
+    snprintf(buf, len, "spmm_warp_kernel slabs of 128/64/32 columns, strided, K=%lld", (long long)K);
+  } else {
+    snprintf(buf, len, "spmm_generic_kernel<%d,4,0> K=%lld", (K & 3) == 0 ? 4 : 1, (long long)K);
+  }
   return HPSPMM_OK;
 }
 
@@ -1491,37 +1509,59 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
                   row_list{nz_id, nz_end, chunk_ri});
 }
 
-// Host-buffer product, pipelined over 32-column slabs when K is a multiple of 32 and K >= 64:
-// C[:, s] = A * B[:, s] needs only slab s of B, so slab s+1 is uploaded (strided 2-D copy)
-// while slab s is multiplied (as a contiguous K = 32 product) and slab s-1 is downloaded.
-// PCIe is full duplex: the downloads hide behind the uploads and the call costs about
-// upload(A) + upload(B) + download(one slab) instead of upload + download of everything.
-static int host_product_slabs(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz,
-                              const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
-                              const float* B, float* C, const hpspmm_opts* opts) {
-  // 64-column slabs when they divide K and leave at least two (256-byte rows copy faster than
-  // 128-byte rows when both directions are busy), else 32
-  const int64_t KS = (K % 64 == 0 && K >= 128) ? 64 : 32;
+// Host-buffer products, pipelined over column slabs: C[:, s] = A * B[:, s] needs only slab s of B,
+// so slab s+1 is uploaded (strided 2-D copy) while slab s is multiplied (as a contiguous product of
+// the slab's width) and slab s-1 is downloaded.  PCIe is full duplex: the downloads hide behind the
+// uploads.  A is uploaded once, in front; the slabs of several products that share A follow one
+// another through the same pipeline, so the whole call costs about
+// upload(A) + upload(all B) + product and download of the last slab.
+namespace {
+struct host_slab {
+  const float* B;   // host, first column of the slab
+  float* C;         // host, first column of the slab
+  int64_t K;        // row stride of the host matrices
+  int64_t width;    // 32 or 64 (or K itself for widths that are not multiples of 32)
+};
+}  // namespace
+
+static int host_products_pipelined(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
+                                   const int32_t* col_idx, const float* vals, const host_slab* slabs, int n_slabs,
+                                   const hpspmm_opts* opts) {
   constexpr int NBUF = 2;
-  const int n_slabs = (int)(K / KS);
   for (int i = 0; i < 3; ++i)
     if (!ctx->pipe_streams[i])
       HPSPMM_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->pipe_streams[i], cudaStreamNonBlocking));
+  // the events live in the context: created once, never leaked by an error path of a call
+  for (int i = 0; i < 1 + 3 * NBUF; ++i)
+    if (!ctx->pipe_events[i])
+      HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->pipe_events[i], cudaEventDisableTiming));
   cudaStream_t s_in = ctx->pipe_streams[0], s_run = ctx->pipe_streams[1], s_out = ctx->pipe_streams[2];
+  cudaEvent_t ev_a = ctx->pipe_events[0];
+  cudaEvent_t* ev_b = ctx->pipe_events + 1;
+  cudaEvent_t* ev_run = ctx->pipe_events + 1 + NBUF;
+  cudaEvent_t* ev_out = ctx->pipe_events + 1 + 2 * NBUF;
+  int64_t wmax = 1;
+  for (int i = 0; i < n_slabs; ++i) wmax = slabs[i].width > wmax ? slabs[i].width : wmax;
   const size_t b_rp = align_up((size_t)(M + 1) * 4, 256);
-  const size_t b_nz = align_up((size_t)nnz * 4, 256);
-  const size_t b_Bs = align_up((size_t)N * KS * 4, 256);
-  const size_t b_Cs = align_up((size_t)M * KS * 4, 256);
+  const size_t b_nz = align_up((size_t)(nnz > 0 ? nnz : 1) * 4, 256);
+  const size_t b_Bs = align_up((size_t)(N > 0 ? N : 1) * wmax * 4, 256);
+  const size_t b_Cs = align_up((size_t)M * wmax * 4, 256);
   int st = hpspmm_ensure_stage(ctx, b_rp + 2 * b_nz + NBUF * (b_Bs + b_Cs));
   if (st != HPSPMM_OK) return st;
   // size the kernel scratch before anything is queued (growing it synchronises the device)
   {
-    const int32_t S = (opts && opts->chunk_nnz > 0) ? (opts->chunk_nnz + 31) / 32 * 32 : hpspmm_default_chunk_nnz(KS, nnz);
-    const int64_t n_chunks = (nnz + S - 1) / S;
-    const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
-    const size_t b_sort = hpspmm_order_scratch_bytes(n_chunks), b_list = hpspmm_row_list_scratch_bytes(M);
-    st = hpspmm_ensure_scratch(ctx, 6 * b_int + align_up((size_t)(n_chunks + 1) * KS * 4, 256) +
-                                        2 * align_up((size_t)(M + 2) * 4, 256) + (b_sort > b_list ? b_sort : b_list));
+    size_t need = 0;
+    for (int i = 0; i < n_slabs; ++i) {
+      const int64_t w = slabs[i].width;
+      const int32_t S = (opts && opts->chunk_nnz > 0) ? (opts->chunk_nnz + 31) / 32 * 32 : hpspmm_default_chunk_nnz(w, nnz);
+      const int64_t n_chunks = (nnz + S - 1) / S;
+      const size_t b_int = align_up((size_t)(n_chunks + 1) * 4, 256);
+      const size_t b_sort = hpspmm_order_scratch_bytes(n_chunks), b_list = hpspmm_row_list_scratch_bytes(M);
+      const size_t want = 6 * b_int + align_up((size_t)(n_chunks + 1) * w * 4, 256) +
+                          2 * align_up((size_t)(M + 2) * 4, 256) + (b_sort > b_list ? b_sort : b_list);
+      need = want > need ? want : need;
+    }
+    st = hpspmm_ensure_scratch(ctx, need);
     if (st != HPSPMM_OK) return st;
   }
   char* base = (char*)ctx->stage;
@@ -1534,13 +1574,6 @@ static int host_product_slabs(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, 
     d_Bs[i] = (float*)(base + b_rp + 2 * b_nz + i * b_Bs);
     d_Cs[i] = (float*)(base + b_rp + 2 * b_nz + NBUF * b_Bs + i * b_Cs);
   }
-  cudaEvent_t ev_a, ev_b[NBUF], ev_run[NBUF], ev_out[NBUF];
-  HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev_a, cudaEventDisableTiming));
-  for (int i = 0; i < NBUF; ++i) {
-    HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev_b[i], cudaEventDisableTiming));
-    HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev_run[i], cudaEventDisableTiming));
-    HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev_out[i], cudaEventDisableTiming));
-  }
   int rc = HPSPMM_OK;
   cudaError_t e = cudaSuccess;
 #define PIPE_TRY(call)                      \
@@ -1548,43 +1581,91 @@ static int host_product_slabs(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, 
     e = (call);                             \
   }
   PIPE_TRY(cudaMemcpyAsync(d_rp, row_ptr, (size_t)(M + 1) * 4, cudaMemcpyHostToDevice, s_in));
-  PIPE_TRY(cudaMemcpyAsync(d_col, col_idx, (size_t)nnz * 4, cudaMemcpyHostToDevice, s_in));
-  PIPE_TRY(cudaMemcpyAsync(d_val, vals, (size_t)nnz * 4, cudaMemcpyHostToDevice, s_in));
+  if (nnz > 0) {
+    PIPE_TRY(cudaMemcpyAsync(d_col, col_idx, (size_t)nnz * 4, cudaMemcpyHostToDevice, s_in));
+    PIPE_TRY(cudaMemcpyAsync(d_val, vals, (size_t)nnz * 4, cudaMemcpyHostToDevice, s_in));
+  }
   PIPE_TRY(cudaEventRecord(ev_a, s_in));
   PIPE_TRY(cudaStreamWaitEvent(s_run, ev_a, 0));
   for (int s = 0; s < n_slabs; ++s) {
     const int buf = s % NBUF;
+    const host_slab& sl = slabs[s];
     // upload slab s once the product that last read this buffer is done
     if (s >= NBUF) PIPE_TRY(cudaStreamWaitEvent(s_in, ev_run[buf], 0));
-    PIPE_TRY(cudaMemcpy2DAsync(d_Bs[buf], KS * 4, B + s * KS, (size_t)K * 4, KS * 4, (size_t)N,
-                               cudaMemcpyHostToDevice, s_in));
+    if (nnz > 0 && N > 0)
+      PIPE_TRY(cudaMemcpy2DAsync(d_Bs[buf], sl.width * 4, sl.B, (size_t)sl.K * 4, sl.width * 4, (size_t)N,
+                                 cudaMemcpyHostToDevice, s_in));
     PIPE_TRY(cudaEventRecord(ev_b[buf], s_in));
     // multiply once the slab has landed and the previous download from this C buffer is done
     PIPE_TRY(cudaStreamWaitEvent(s_run, ev_b[buf], 0));
     if (s >= NBUF) PIPE_TRY(cudaStreamWaitEvent(s_run, ev_out[buf], 0));
     if (rc == HPSPMM_OK && e == cudaSuccess)
-      rc = hpspmm_spmm_csr_f32(ctx, nullptr, M, N, KS, nnz, d_rp, d_col, d_val, d_Bs[buf], d_Cs[buf], opts,
+      rc = hpspmm_spmm_csr_f32(ctx, nullptr, M, N, sl.width, nnz, d_rp, d_col, d_val, d_Bs[buf], d_Cs[buf], opts,
                                (hpspmm_stream)s_run);
     PIPE_TRY(cudaEventRecord(ev_run[buf], s_run));
     // download
     PIPE_TRY(cudaStreamWaitEvent(s_out, ev_run[buf], 0));
-    PIPE_TRY(cudaMemcpy2DAsync(C + s * KS, (size_t)K * 4, d_Cs[buf], KS * 4, KS * 4, (size_t)M,
+    PIPE_TRY(cudaMemcpy2DAsync(sl.C, (size_t)sl.K * 4, d_Cs[buf], sl.width * 4, sl.width * 4, (size_t)M,
                                cudaMemcpyDeviceToHost, s_out));
     PIPE_TRY(cudaEventRecord(ev_out[buf], s_out));
   }
 #undef PIPE_TRY
-  // drain all three streams whatever happened, then release the events
+  // drain all three streams whatever happened
   cudaError_t e1 = cudaStreamSynchronize(s_in), e2 = cudaStreamSynchronize(s_run), e3 = cudaStreamSynchronize(s_out);
-  cudaEventDestroy(ev_a);
-  for (int i = 0; i < NBUF; ++i) {
-    cudaEventDestroy(ev_b[i]);
-    cudaEventDestroy(ev_run[i]);
-    cudaEventDestroy(ev_out[i]);
-  }
   if (rc != HPSPMM_OK) return rc;
   if (e == cudaSuccess) e = e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3);
   if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "host-buffer product pipeline", e);
   return HPSPMM_OK;
+}
+
+// slabs of one product: 64 columns when they divide K and leave at least two (256-byte rows copy
+// faster than 128-byte rows when both directions are busy), else 32; a width that is no multiple of 32
+// travels whole
+static int append_slabs(host_slab* out, int cap, int n, const float* B, float* C, int64_t K) {
+  if (K % 32 != 0) {
+    if (n >= cap) return -1;
+    out[n++] = host_slab{B, C, K, K};
+    return n;
+  }
+  const int64_t w = (K % 64 == 0 && K >= 128) ? 64 : 32;
+  for (int64_t off = 0; off < K; off += w) {
+    if (n >= cap) return -1;
+    out[n++] = host_slab{B + off, C + off, K, w};
+  }
+  return n;
+}
+
+static int host_product_slabs(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz,
+                              const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
+                              const float* B, float* C, const hpspmm_opts* opts) {
+  host_slab slabs[64];
+  const int n = append_slabs(slabs, 64, 0, B, C, K);
+  if (n < 0) return HPSPMM_ERR_UNSUPPORTED;
+  return host_products_pipelined(ctx, M, N, nnz, row_ptr, col_idx, vals, slabs, n, opts);
+}
+
+int hpspmm_spmm_csr_f32_host_multi(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
+                                   const int32_t* col_idx, const float* vals, int32_t n_products, const int64_t* Ks,
+                                   const float* const* Bs, float* const* Cs, const hpspmm_opts* opts) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
+  HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "bad size");
+  HPSPMM_REQUIRE(ctx, n_products >= 0 && n_products <= 16, "between 0 and 16 products per call");
+  HPSPMM_REQUIRE(ctx, n_products == 0 || (Ks && Bs && Cs), "null product list");
+  HPSPMM_REQUIRE(ctx, row_ptr != nullptr, "null row_ptr");
+  HPSPMM_REQUIRE(ctx, nnz == 0 || (col_idx && vals), "null operand");
+  if (M == 0 || n_products == 0) return HPSPMM_OK;
+  const int algo = opts ? opts->algo : HPSPMM_ALGO_AUTO;
+  HPSPMM_REQUIRE(ctx, algo != HPSPMM_ALGO_ROW_SPLIT, "the multi-product entry runs the balanced kernels only");
+  host_slab slabs[16 * 16];
+  int n = 0;
+  for (int i = 0; i < n_products; ++i) {
+    HPSPMM_REQUIRE(ctx, Ks[i] >= 1 && Ks[i] <= 512, "K must be between 1 and 512");
+    HPSPMM_REQUIRE(ctx, Cs[i] != nullptr && (nnz == 0 || Bs[i] != nullptr), "null dense operand");
+    n = append_slabs(slabs, 16 * 16, n, Bs[i], Cs[i], Ks[i]);
+    if (n < 0) return HPSPMM_ERR_UNSUPPORTED;
+  }
+  hpspmm_device_guard guard(ctx->device);
+  return host_products_pipelined(ctx, M, N, nnz, row_ptr, col_idx, vals, slabs, n, opts);
 }
 
 int hpspmm_spmm_csr_f32_host(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz,
@@ -1735,6 +1816,17 @@ extern "C" int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M,
   if (device_ordinal < 0 || device_ordinal >= kMaxStaticDevices) {
     write_err(err_buf, err_len, "device ordinal out of range");
     return HPSPMM_ERR_INVALID;
+  }
+  {
+    // a device the process cannot see must be refused here: making it current below would fail
+    // silently and the array's address would be looked up on whichever device happens to be current
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device_ordinal >= count) {
+      char msg[128];
+      snprintf(msg, sizeof(msg), "device ordinal %d does not exist (%d visible)", device_ordinal, count);
+      write_err(err_buf, err_len, msg);
+      return HPSPMM_ERR_INVALID;
+    }
   }
   hpspmm_ctx local;  // a stack stand-in for a context: no allocation behind it
   memset(&local, 0, sizeof(local));

@@ -88,9 +88,13 @@ int main(int argc, char** argv) {
     Matrix d_res_coo = full({num, k}, Device(kCUDA), DataType(kFloat), 0.0);
 
     float t = 0.f;
-    HPSpMM(d_csr, d_dense, d_res_ge, t, launches, WARMUP_NUM_CUDA, HPSPMM_ALGO_ROW_SPLIT);
+    // the reference's two CSR / COO entry points by their own names (test/test_all.cpp:91-92, :101-102) ...
+    GESpMM(d_csr, d_dense, d_res_ge, t, launches);
     info.spmm_ge_time_ = t;
-    std::cout << "GE-shaped SpMM time: " << t << " ms" << std::endl;
+    // ... the row-split arithmetic of the reference's GESpMM kernels, for the bit-exact check below ...
+    Matrix d_res_rs = full({num, k}, Device(kCUDA), DataType(kFloat), 0.0);
+    GESpMM_rowsplit(d_csr, d_dense, d_res_rs, t, launches < 3 ? launches : 3, 1);
+    // ... and the balanced kernel under its own name
     HPSpMM(d_csr, d_dense, d_res_hp, t, launches);
     info.spmm_hp_time_ = t;
     std::cout << "HP-SpMM time: " << t << " ms" << std::endl;
@@ -113,7 +117,8 @@ int main(int argc, char** argv) {
       for (int i = 0; i < EXE_NUM_CPU; ++i) cpu_csr_spmm(h_csr, dense_mat_cpu, c_ref);
       ct.Stop();
       info.spmm_cpu_time_ = ct.Elapsed() / EXE_NUM_CPU;
-      if (ExpectEqualDenseWithError(d_res_ge, c_ref) != 0.0) rc = 1;          // row split: bit exact
+      if (ExpectEqualDenseWithError(d_res_rs, c_ref) != 0.0) rc = 1;          // row split: bit exact
+      if (ExpectEqualDenseWithError(d_res_ge, c_ref, "", 1e-2) >= 1e-2) rc = 1;
       if (ExpectEqualDenseWithError(d_res_hp, c_ref, "", 1e-2) >= 1e-2) rc = 1;
       if (ExpectEqualDenseWithError(d_res_coo, c_ref, "", 1e-2) >= 1e-2) rc = 1;
     }

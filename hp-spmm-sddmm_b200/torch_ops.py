@@ -22,17 +22,8 @@ import torch
 from . import Context, Layer
 
 _layers = {}
-_contexts = {}
 _ids = itertools.count(1)
-_lock = threading.Lock()
-
-
-def _context_for(device_index):
-    with _lock:
-        ctx = _contexts.get(device_index)
-        if ctx is None:
-            ctx = _contexts[device_index] = Context(device_index)
-        return ctx
+_lock = threading.Lock()   # guards the registry of layers
 
 
 def _entry(layer_id):
@@ -147,23 +138,30 @@ class TorchLayer:
         self.M, self.N, self.nnz, self.max_K = int(M), int(N), int(vals.numel()), int(max_K)
         self.row_ptr, self.col_idx, self.vals = row_ptr, col_idx, vals
         dev = row_ptr.device
-        ctx = _context_for(dev.index if dev.index is not None else torch.cuda.current_device())
+        # One context per layer.  A context owns scratch and a flag that plan building uses (also lazily, on
+        # the first product of a new width class), and calls that share a context must not overlap on the
+        # GPU: with a context of their own, two layers driven from different streams or threads cannot meet
+        # there.  Products of ONE layer still must not overlap with each other.
+        ctx = Context(dev.index if dev.index is not None else torch.cuda.current_device())
         with torch.cuda.device(dev):
             v = vals.detach()
             layer = Layer(ctx, self.M, self.N, self.nnz, row_ptr.data_ptr(), col_idx.data_ptr(), v.data_ptr(),
                           self.max_K, torch.cuda.current_stream().cuda_stream)
-        self.layer_id = next(_ids)
-        _layers[self.layer_id] = {"layer": layer, "M": self.M, "N": self.N, "nnz": self.nnz,
-                                  "vals_key": (v.data_ptr(), v._version), "vals_ref": v,
-                                  "keep": (row_ptr, col_idx)}
+        with _lock:
+            self.layer_id = next(_ids)
+            _layers[self.layer_id] = {"layer": layer, "ctx": ctx, "M": self.M, "N": self.N, "nnz": self.nnz,
+                                      "vals_key": (v.data_ptr(), v._version), "vals_ref": v,
+                                      "keep": (row_ptr, col_idx)}
 
     def __call__(self, H, vals=None):
         return layer_forward(H, self.vals if vals is None else vals, self.layer_id)
 
     def close(self):
-        e = _layers.pop(self.layer_id, None)
+        with _lock:
+            e = _layers.pop(self.layer_id, None)
         if e:
             e["layer"].close()
+            e["ctx"].close()
 
     def __del__(self):
         try:

@@ -153,6 +153,10 @@ HPSPMM_API int hpspmm_plan_destroy(hpspmm_ctx* ctx, hpspmm_plan* plan);
 HPSPMM_API int hpspmm_plan_info(const hpspmm_plan* plan, int64_t* n_chunks,
                                 int64_t* n_split_chunks, int64_t* chunk_nnz,
                                 int64_t* scratch_bytes);
+/* Name and template arguments of the kernel hpspmm_spmm_csr_f32 launches for width K with this
+ * plan (plan may be NULL) and L2 hint setting, as a string: profiler captures are filed under it. */
+HPSPMM_API int hpspmm_spmm_kernel_signature(const hpspmm_plan* plan, int64_t K, int32_t b_l2_hint,
+                                            char* buf, size_t len);
 /* Device pointers to the plan's tables, for inspection: chunk_start[n_chunks + 1] (first
  * entry of every chunk), chunk_row[n_chunks] (row holding that entry), chunk_order[n_chunks]
  * (the chunk ids in the order in which warps take them: a permutation of 0..n_chunks-1). */
@@ -198,16 +202,30 @@ HPSPMM_API int hpspmm_spmm_csr_f32_static_scratch(int device_ordinal, int64_t M,
 /* Same product with HOST buffers: copies A and B to the device, runs the product,
  * copies C back, synchronises.  When K is a multiple of 32 and at least 64 the call is
  * pipelined over 32- or 64-column slabs of B and C (uploads, products and downloads overlap on
- * three internal streams, PCIe being full duplex); each slab is a K = 32 product, so the
- * rounding of rows split across chunks can differ from the device-pointer entry point in
- * the last bits.  This is the call the end-to-end figure is timed
- * through; it is what the reference's driver does around GESpMM
- * (test/test_all.cpp:44-60 upload, :91-92 product) plus the download the
- * reference only performs inside its disabled checker (spmm/utils/compare.cpp:6-7). */
+ * three internal streams, PCIe being full duplex); each slab is a product of the slab's width, so
+ * the rounding of rows split across chunks can differ from the device-pointer entry point in
+ * the last bits.  The overlap needs page-locked host buffers (hpspmm_host_alloc_pinned or the
+ * caller's own): from pageable memory the copies are staged and serialised by the driver and the
+ * call degrades to upload, product, download one after the other.  It is what the reference's
+ * driver does around GESpMM (test/test_all.cpp:44-60 upload, :91-92 product) plus the download
+ * the reference only performs inside its disabled checker (spmm/utils/compare.cpp:6-7). */
 HPSPMM_API int hpspmm_spmm_csr_f32_host(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K,
                                         int64_t nnz, const int32_t* row_ptr,
                                         const int32_t* col_idx, const float* vals,
                                         const float* B, float* C, const hpspmm_opts* opts);
+
+/* Several products that share A, with HOST buffers: C_i = A * B_i for i < n_products (at most 16),
+ * B_i being N x Ks[i] and C_i M x Ks[i].  A crosses PCIe once; the column slabs of all the
+ * products then follow one another through one upload / product / download pipeline, so the
+ * call costs about upload(A) + upload(all B_i) + product and download of the last slab.  This
+ * is the shape of the reference's driver, which uploads one graph and then runs its products
+ * at K = 32, 64, 128 ... on it (test/test_all.cpp:44-60, run.sh).  Widths from 1 to 512;
+ * balanced kernels only.  Synchronises.  Pinned host buffers are needed for the overlap. */
+HPSPMM_API int hpspmm_spmm_csr_f32_host_multi(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz,
+                                              const int32_t* row_ptr, const int32_t* col_idx,
+                                              const float* vals, int32_t n_products,
+                                              const int64_t* Ks, const float* const* Bs,
+                                              float* const* Cs, const hpspmm_opts* opts);
 
 /* ---- COO SpMM: C += A * B --------------------------------------------------------
  * Replaces LBSpMM (include/spmm/mm/spmm_kernel.h:20, spmm/mm/spmm_kernel.cu:733-768,
@@ -396,13 +414,15 @@ HPSPMM_API int hpspmm_shard_needed_rows(int64_t nnz_local, const int32_t* col_id
  *   world > 1).  hpspmm_comm_unique_id on one rank, its 128 bytes carried to the others by any
  *   means the host program has, then hpspmm_comm_create on every rank (collective).
  * shard plan (collective, synchronises): from the shard's HOST row_ptr / col_idx it lists the rows
- *   of B the shard references per owner (HPSPMM_EXCHANGE_NEEDED_ROWS) or takes all of them
- *   (HPSPMM_EXCHANGE_ALL_ROWS, the plain all-gather), renumbers the shard's columns into that list,
+ *   of B the shard references per owner (HPSPMM_EXCHANGE_NEEDED_ROWS, and ..._NCCL, which differs in the
+ *   transport only) or takes all of them (HPSPMM_EXCHANGE_ALL_ROWS, the plain all-gather), renumbers the shard's columns into that list,
  *   tells every owner which rows to send, and keeps device copies of row_ptr and the renumbered
  *   columns.  Every rank must pass the same b_bounds, max_K and exchange mode.
- * exchange_begin: enqueues, on the plan's own stream and after what `stream` holds now, the packing
- *   of the rows the other ranks need and one grouped NCCL send / receive; remote rows land in this
- *   GPU's own memory.  product: waits (stream event) for that slot's rows, then runs the local
+ * exchange_begin: enqueues, on the plan's own stream and after what `stream` holds now, the transfer
+ *   of the rows the other ranks need: one kernel that stores them into the receivers' operands over
+ *   NVLink followed by a four-byte NCCL all-reduce as the completion signal, or (the NCCL transports) a
+ *   packing kernel and one grouped send / receive.  Remote rows land in this GPU's own memory before any
+ *   product reads them.  A slot must not be begun again before its product has been enqueued.  product: waits (stream event) for that slot's rows, then runs the local
  *   product on `stream`.  Slots 0..3 are independent buffers: begin several products, then multiply
  *   them in turn, and each exchange overlaps the previous product.  All ranks must issue their begins
  *   in the same order.  The first use of a slot (or a wider K on it) allocates and synchronises.
@@ -412,7 +432,12 @@ HPSPMM_API int hpspmm_shard_needed_rows(int64_t nnz_local, const int32_t* col_id
 typedef struct hpspmm_comm hpspmm_comm;
 typedef struct hpspmm_shard_plan hpspmm_shard_plan;
 enum { HPSPMM_COMM_ID_BYTES = 128 };
-enum { HPSPMM_EXCHANGE_NEEDED_ROWS = 0, HPSPMM_EXCHANGE_ALL_ROWS = 1 };
+enum {
+  HPSPMM_EXCHANGE_NEEDED_ROWS = 0,      /* referenced rows only, pushed into the receivers' operands by
+                                           peer stores (CUDA IPC mappings), NCCL only as the signal      */
+  HPSPMM_EXCHANGE_ALL_ROWS = 1,         /* plain all-gather of B over NCCL send / receive               */
+  HPSPMM_EXCHANGE_NEEDED_ROWS_NCCL = 2  /* referenced rows only, packed and sent by ncclSend / ncclRecv */
+};
 HPSPMM_API int hpspmm_comm_unique_id(unsigned char* id_out);
 HPSPMM_API int hpspmm_comm_create(hpspmm_ctx* ctx, int32_t world, int32_t rank,
                                   const unsigned char* id, hpspmm_comm** out);
@@ -447,6 +472,14 @@ HPSPMM_API double hpspmm_row_length_cv(int64_t M, const int32_t* row_ptr_host);
 HPSPMM_API double hpspmm_spmm_algorithmic_bytes(int64_t M, int64_t N_ref, int64_t K, int64_t nnz);
 HPSPMM_API double hpspmm_sddmm_algorithmic_bytes(int64_t M_ref, int64_t N_ref, int64_t K,
                                                  int64_t M, int64_t nnz);
+
+/* ---- diagnostics: allocation-failure seam ------------------------------------------------------------
+ * Test hook: the nth device allocation the library makes from now on (1 = the next one) reports an
+ * out-of-memory error without touching the device, once; 0 disarms.  Process-wide.  Lets a test see
+ * that every entry point that allocates returns HPSPMM_ERR_OOM, frees what it had already taken and
+ * leaves the context usable -- where the reference ignores the result of cudaMalloc altogether
+ * (spmm/starml/basic/allocator_cuda.cpp:5-13). */
+HPSPMM_API int hpspmm_debug_fail_device_alloc(int64_t nth);
 
 /* ---- diagnostics: load-path ceilings ---------------------------------------------------------------
  * Times the gather shape of the product kernels alone (lane groups of row_bytes / 16 lanes,

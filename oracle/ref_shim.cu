@@ -5,6 +5,7 @@
 //
 // Nothing of the reference is copied: this file only includes its headers and calls its
 // entry points (include/spmm/mm/spmm_kernel.h:19-21).
+#include <chrono>
 #include <cstring>
 
 #include "spmm/mm/spmm_kernel.h"
@@ -84,6 +85,49 @@ __attribute__((visibility("default"))) int ref_lbspmm(int m, int n, int k, int n
   Matrix hC = dC.to(kCPU);
   std::memcpy(C_out, hC.data<float>(), sizeof(float) * (size_t)m * (size_t)k);
   if (ms_out) *ms_out = ms;
+  return 0;
+}
+
+// The same LBSpMM call with its three phases timed apart, each phase being the reference's own code:
+// upload = Matrix::to(kCUDA) of the COO arrays and of B plus the zero-filled C (cudaMalloc + synchronous
+// copies from pageable memory, spmm/starml/operators/cuda/copy_kernel.cu:7-41), kernel_ms = the mean the
+// reference's GpuTimer reports over its EXE_NUM_CUDA launches, download = Matrix::to(kCPU) of C.  Building
+// the host Matrix objects from the caller's arrays (this shim's own copies) is outside all three.
+__attribute__((visibility("default"))) int ref_lbspmm_phases(int m, int n, int k, int nnz_padded, const int* row_idx,
+                                                             const int* col_idx, const float* vals, const float* B,
+                                                             float* C_out, float* kernel_ms, double* upload_s,
+                                                             double* download_s) {
+  using clock = std::chrono::steady_clock;
+  COO_Matrix h;
+  h.num_rows_ = m;
+  h.num_cols_ = n;
+  h.num_nonzeros_ = nnz_padded;
+  h.row_indices_ = host_ints(row_idx, nnz_padded);
+  h.column_indices_ = host_ints(col_idx, nnz_padded);
+  h.values_ = host_floats(vals, nnz_padded, 0);
+  Matrix hB = host_floats(B, n, k);
+  if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  const auto t0 = clock::now();
+  COO_Matrix d = h;
+  d.row_indices_ = h.row_indices_.to(kCUDA);
+  d.column_indices_ = h.column_indices_.to(kCUDA);
+  d.values_ = h.values_.to(kCUDA);
+  Matrix dB = hB.to(kCUDA);
+  Matrix dC = full({m, k}, Device(kCUDA), DataType(kFloat), 0.0);
+  fill_matrix(dC, 0.0f);
+  if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  const auto t1 = clock::now();
+  float ms = 0.f;
+  LBSpMM(d, dB, dC, ms);
+  if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  const auto t2 = clock::now();
+  Matrix hC = dC.to(kCPU);
+  if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  const auto t3 = clock::now();
+  std::memcpy(C_out, hC.data<float>(), sizeof(float) * (size_t)m * (size_t)k);
+  if (kernel_ms) *kernel_ms = ms;
+  if (upload_s) *upload_s = std::chrono::duration<double>(t1 - t0).count();
+  if (download_s) *download_s = std::chrono::duration<double>(t3 - t2).count();
   return 0;
 }
 

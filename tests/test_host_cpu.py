@@ -172,3 +172,20 @@ def test_row_order_reader(pkg, tmp_path):
             pkg.read_row_order(str(bad), 4)
     with pytest.raises(pkg.HpspmmError):
         pkg.read_row_order(str(tmp_path / "missing"), 4)
+
+
+def test_numpy_restatement_of_the_generator_matches_the_library(pkg):
+    """tests/helpers.uniform_rows regenerates rows of a device-filled operand on the host; it must equal the
+    library's own host generator bit for bit."""
+    from helpers import uniform_at, uniform_rows
+    for seed, stream, lo, hi in ((2, 132, -1.0, 1.0), (9, 7, 0.0, 1.0), (4, 128, -0.5, 2.5)):
+        want = pkg.host_fill_uniform(5000, seed, stream, lo, hi)
+        assert np.array_equal(uniform_at(seed, stream, np.arange(5000), lo, hi), want)
+    K = 128
+    full = pkg.host_fill_uniform(300 * K, 4, 128, -1.0, 1.0).reshape(300, K)
+    rows = np.array([0, 17, 299, 17])
+    assert np.array_equal(uniform_rows(4, 128, rows, K, -1.0, 1.0), full[rows])
+    # far beyond 2^31 elements: compare with a window generated by the library at that offset
+    big = np.array([2 ** 31 + 5, 2 ** 32 + 1, 17_499_999 * 128 + 127], dtype=np.uint64)
+    got = uniform_at(9, 1, big, -1.0, 1.0)
+    assert got.dtype == np.float32 and np.all((got >= -1.0) & (got < 1.0))

@@ -1,42 +1,51 @@
-"""The large benchmark configurations at full size, checked through size-independent properties.
+"""The large benchmark configurations at full size, checked through sampled rows.
 
-With B = ones every element of row r of C equals the sum of that row's values, whatever the
-graph size; sampled rows (the heaviest, the first, the last, rows behind the 2^31-element mark)
-are brought back and compared with float64 row sums.  The uniform sparse case is also compared with the oracle.
+B is filled on the device by the library's counter-based generator, so the rows of B that a sampled row
+of A needs can be regenerated on the host (helpers.uniform_rows) without holding the 8.6 GB operand: every
+sampled row of C (the heaviest, the first, the last, rows behind the 2^31-element mark, rows whose columns
+lie behind it) is compared with a float64 sum over those regenerated rows.  A wrong 64-bit offset into B or
+C shows up as a wrong row.  The uniform sparse case is also compared with the oracle in full.
 """
 import numpy as np
 import pytest
 
-from helpers import check_against_f64
+from helpers import BACKWARD_TOL, check_against_f64, uniform_rows
 
 pytestmark = pytest.mark.gpu
 
 
-def _rows_vs_rowsums(ctx, pkg, g, K, sample_rows, use_plan=True):
+def _rows_vs_f64(ctx, pkg, g, K, sample_rows, seed, stream_id, use_plan=True):
     M, N, nnz = g["M"], g["N"], g["nnz"]
     d_rp, d_ci, d_v = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"]), ctx.upload(g["vals"])
     d_B = ctx.alloc((N, K), np.float32)
-    ctx.fill(d_B, N * K, 1.0)
+    ctx.fill_uniform(d_B, N * K, seed, stream_id, -1.0, 1.0)
     d_C = ctx.alloc((M, K), np.float32)
     ctx.fill(d_C, M * K, -5.0)                      # stale data must be overwritten everywhere
     plan = ctx.plan_create(M, nnz, d_rp, K, N=N, col_idx=d_ci) if use_plan else None
     ctx.spmm_csr(M, N, K, nnz, d_rp, d_ci, d_v, d_B, d_C, plan=plan)
     ctx.stream_sync()
     rp = g["row_ptr"].astype(np.int64)
-    v64 = g["vals"].astype(np.float64)
+    worst = 0.0
     for r in sample_rows:
         got = np.empty(K, dtype=np.float32)
         ctx.memcpy_d2h(got, d_C.ptr + int(r) * K * 4)
         ctx.stream_sync()
-        seg = v64[rp[r]:rp[r + 1]]
-        want, scale = seg.sum(), np.abs(seg).sum()
-        assert np.all(np.abs(got - want) <= 1e-5 * max(scale, 1e-30)), (r, got[:4], want)
-        if len(seg) == 0:
-            assert np.all(got == 0)
+        cols = g["col_idx"][rp[r]:rp[r + 1]]
+        if len(cols) == 0:
+            assert np.all(got == 0), r
+            continue
+        vals = g["vals"][rp[r]:rp[r + 1]].astype(np.float64)
+        Brows = uniform_rows(seed, stream_id, cols, K, -1.0, 1.0).astype(np.float64)
+        want = vals @ Brows
+        scale = np.abs(vals) @ np.abs(Brows)
+        err = float(np.max(np.abs(got - want) / np.maximum(scale, 1e-30)))
+        worst = max(worst, err)
+        assert err <= BACKWARD_TOL, (r, len(cols), err, got[:4], want[:4])
     if plan:
         ctx.plan_destroy(plan)
     for b in (d_rp, d_ci, d_v, d_B, d_C):
         b.free()
+    return worst
 
 
 def _sample(g, extra=()):
@@ -55,7 +64,7 @@ def test_cfg3_erdos_renyi_full_size(gpu_ctx, pkg, oracle):
     ctx = gpu_ctx
     g = pkg.gen_erdos_renyi(2_450_000, 2_450_000, 50.0, seed=3)
     assert 121_000_000 < g["nnz"] < 124_000_000
-    _rows_vs_rowsums(ctx, pkg, g, 64, _sample(g))
+    _rows_vs_f64(ctx, pkg, g, 64, _sample(g), 3, 64)
     K, M, N, nnz = 64, g["M"], g["N"], g["nnz"]
     B = pkg.host_fill_uniform(N * K, 3, 64, -1.0, 1.0).reshape(N, K)
     d_rp, d_ci, d_v, d_B = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"]), ctx.upload(g["vals"]), ctx.upload(B)
@@ -68,21 +77,37 @@ def test_cfg3_erdos_renyi_full_size(gpu_ctx, pkg, oracle):
         b.free()
 
 
+def _rows_with_columns_from(g, first_col, count):
+    """Rows that hold an entry whose column is at least first_col."""
+    pos = np.flatnonzero(g["col_idx"] >= first_col)
+    if len(pos) == 0:
+        return []
+    pick = pos[np.linspace(0, len(pos) - 1, count).astype(np.int64)]
+    return [int(r) for r in np.searchsorted(g["row_ptr"], pick, side="right") - 1]
+
+
 def test_offsets_beyond_2_31_elements(gpu_ctx, pkg):
-    """N*K and M*K above 2^31 elements: the dense operands need 64-bit offsets."""
+    """N*K and M*K above 2^31 elements: the dense operands need 64-bit offsets, into C (rows behind the mark)
+    and into B (columns behind the mark)."""
     M = N = 17_500_000
+    K = 128
     g = pkg.gen_uniform_degree(M, N, 0, 6, seed=9, vals_kind=pkg.VALS_UPM1)
-    assert M * 128 > 2 ** 31
-    last = [M - 1 - i for i in range(0, 200, 7)]       # rows whose element offset exceeds 2^31
-    _rows_vs_rowsums(gpu_ctx, pkg, g, 128, _sample(g, last), use_plan=False)
+    mark = 2 ** 31 // K                                  # first row / column whose element offset exceeds 2^31
+    assert M > mark
+    last = [M - 1 - i for i in range(0, 200, 7)]         # rows of C behind the mark
+    far = _rows_with_columns_from(g, mark, 40)           # rows of A that read B behind the mark
+    assert len(far) == 40 and all(np.any(g["col_idx"][g["row_ptr"][r]:g["row_ptr"][r + 1]] >= mark) for r in far)
+    _rows_vs_f64(gpu_ctx, pkg, g, K, _sample(g, last + far), 9, 1, use_plan=False)
 
 
 def test_cfg4_rmat_scale24_k128(gpu_ctx, pkg):
-    """Large skewed case: R-MAT scale 24 (about 263 M entries, max degree > 10^5), K = 128."""
+    """Large skewed case: R-MAT scale 24 (about 263 M entries, max degree > 10^5), K = 128, B = 8.6 GB of U(-1,1)
+    (N*K = 2^31 elements exactly: the last rows of B and C sit at byte offsets beyond 2^33)."""
     g = pkg.gen_rmat(24, 16, seed=4)
     deg = np.diff(g["row_ptr"])
     assert g["M"] == 1 << 24 and g["nnz"] > 250_000_000 and deg.max() > 100_000
-    _rows_vs_rowsums(gpu_ctx, pkg, g, 128, _sample(g))
+    far = _rows_with_columns_from(g, g["N"] - 4096, 20)  # rows that read the last rows of B
+    _rows_vs_f64(gpu_ctx, pkg, g, 128, _sample(g, far), 4, 128)
 
 
 def test_cfg5_gnn_layer_full_size(gpu_ctx, pkg, oracle):

@@ -22,7 +22,7 @@ def _shard(pkg, g, world, rank):
     return bounds, lo, hi, np.ascontiguousarray(rp), np.ascontiguousarray(ci), np.ascontiguousarray(v)
 
 
-@pytest.mark.parametrize("exchange", [0, 1])
+@pytest.mark.parametrize("exchange", [0, 1, 2])
 def test_world_one_matches_plain_product(gpu_ctx, pkg, oracle, exchange):
     from helpers import check_against_f64
     ctx = gpu_ctx
@@ -32,7 +32,7 @@ def test_world_one_matches_plain_product(gpu_ctx, pkg, oracle, exchange):
     sp = pkg.ShardedSpmm(ctx, 1, 0, None, M, N, rp, ci, bounds, 128, exchange=exchange)
     info = sp.info()
     assert info["rows_received"] == 0 and info["rows_sent"] == 0
-    assert info["rows_local"] == (len(np.unique(ci)) if exchange == 0 else N)
+    assert info["rows_local"] == (len(np.unique(ci)) if exchange != 1 else N)
     d_v = ctx.upload(v)
     d_rp, d_ci = ctx.upload(rp), ctx.upload(ci)
     for K in (32, 64, 128, 20):
@@ -70,10 +70,15 @@ def test_slots_overlap_and_reuse(gpu_ctx, pkg, oracle):
         for K in Ks:
             ref, abs_sum = oracle.spmm_f64(rp, ci, v, Bs[K])
             check_against_f64(dC[K].to_host(), ref, abs_sum, "slots step %d K=%d" % (step, K))
-    # a product on a slot nothing was begun on is refused
+    # a product on a slot nothing was begun on is refused, and so is a second begin before the product
     with pytest.raises(pkg.HpspmmError) as e:
         sp.product(3, 32, d_v, dC[32])
     assert e.value.status == pkg.ERR_INVALID
+    sp.begin(0, 32, dB[32])
+    with pytest.raises(pkg.HpspmmError) as e:
+        sp.begin(0, 32, dB[32])
+    assert e.value.status == pkg.ERR_INVALID
+    sp.product(0, 32, d_v, dC[32])
     with pytest.raises(pkg.HpspmmError):
         sp.begin(4, 32, dB[32])
     sp.close()
@@ -122,13 +127,13 @@ def _rank_main(rank, world, exchange, out_dir):
     d_v = ctx.upload(v)
     Ks = (32, 64, 128)
     info = sp.info()
-    for step in range(2):
+    for step in range(4):
         dB, dC = {}, {}
         for K in Ks:
             B_own = pkg.host_fill_uniform(N * K, 31 + step, K, -1.0, 1.0).reshape(N, K)[lo:hi]
             dB[K] = ctx.upload(np.ascontiguousarray(B_own))
             dC[K] = ctx.alloc((hi - lo, K), np.float32)
-        if step == 0:
+        if step % 2 == 0:
             for K in Ks:                       # one call per product
                 sp.spmm(K, d_v, dB[K], dC[K])
         else:
@@ -144,7 +149,7 @@ def _rank_main(rank, world, exchange, out_dir):
     ctx.close()
 
 
-@pytest.mark.parametrize("exchange", [0, 1])
+@pytest.mark.parametrize("exchange", [0, 1, 2])
 def test_two_gpu_exchange_and_product(tmp_path, pkg, oracle, exchange):
     import torch
     if torch.cuda.device_count() < 2:
@@ -164,7 +169,7 @@ def test_two_gpu_exchange_and_product(tmp_path, pkg, oracle, exchange):
         assert p.exitcode == 0
     g = pkg.gen_rmat(14, 16, seed=31)
     N = g["N"]
-    for step in range(2):
+    for step in range(4):                      # four steps: both buffers of every slot are used twice
         for K in (32, 64, 128):
             B = pkg.host_fill_uniform(N * K, 31 + step, K, -1.0, 1.0).reshape(N, K)
             ref, abs_sum = oracle.spmm_f64(g["row_ptr"], g["col_idx"], g["vals"], B)
@@ -175,7 +180,7 @@ def test_two_gpu_exchange_and_product(tmp_path, pkg, oracle, exchange):
         rows_local, rows_received, rows_sent, distinct, others = np.load(tmp_path / ("info_%d.npy" % r))
         recv += rows_received
         sent += rows_sent
-        if exchange == 0:
+        if exchange != 1:
             assert rows_local == distinct and rows_received < others
         else:
             assert rows_local == N and rows_received == others

@@ -162,3 +162,63 @@ def test_degenerate_shards(pkg):
     assert sum(int(rp[b[i + 1]] - rp[b[i]]) for i in range(4)) == 5
     empty = np.zeros(7, dtype=np.int32)
     assert list(pkg.shard_bounds(empty, 3)) == [0, 0, 0, 6]
+
+
+def _leaving_rank_main(rank, world, port, out_dir):
+    """Rank 1 leaves between two steps (an exception on the host, nothing in flight); rank 0's next exchange
+    must end with an error after the process group's timeout instead of waiting for ever."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import datetime
+    import importlib
+    import time
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    import oracle_lib
+    pkg = entry.load_package()
+    sharded = importlib.import_module(pkg.__name__ + ".sharded")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    g = pkg.gen_rmat(9, 8, seed=29)
+    N, K = g["N"], 32
+    bounds = pkg.shard_bounds(g["row_ptr"], world)
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    rp, ci, v = pkg.shard_csr(g["row_ptr"], g["col_idx"], g["vals"], lo, hi)
+    H = pkg.host_fill_uniform(N * K, 29, 1, -1.0, 1.0).reshape(N, K)
+    H_own = torch.from_numpy(np.ascontiguousarray(H[lo:hi]))
+    layer = sharded.ShardedLayer(_OracleLocal(oracle_lib, rp, ci, v, hi - lo, N), N, bounds, rank, world)
+    layer.forward(H_own)                       # step 1: everybody takes part
+    dist.barrier()
+    if rank == 1:
+        open(os.path.join(out_dir, "rank1_left"), "w").close()
+        os._exit(17)                           # leaves without a word, between steps
+    t0 = time.time()
+    try:
+        layer.forward(H_own)                   # step 2: the partner is gone
+        outcome = "completed"
+    except Exception as exc:                   # gloo reports the lost peer or the timeout
+        outcome = "error: %s" % type(exc).__name__
+    with open(os.path.join(out_dir, "rank0_outcome"), "w") as fh:
+        fh.write("%s after %.1f s" % (outcome, time.time() - t0))
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_ends_the_next_exchange_with_an_error(tmp_path):
+    import multiprocessing
+    ctx = multiprocessing.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_leaving_rank_main, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(90)
+    alive = [p.is_alive() for p in procs]
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    assert not any(alive), "a rank hung after its partner left"
+    assert (tmp_path / "rank1_left").exists() and procs[1].exitcode == 17
+    outcome = (tmp_path / "rank0_outcome").read_text()
+    assert outcome.startswith("error"), outcome

@@ -134,15 +134,34 @@ def test_overwrites_stale_output_and_linearity(gpu_ctx, pkg, oracle):
     assert np.allclose(C3, C1 + C2, rtol=1e-4, atol=1e-4)              # linear in B
 
 
-def test_full_size_cfg2_k32(gpu_ctx, pkg, oracle):
-    """The power-law benchmark graph (R-MAT scale 20) at full size, K=32, against the oracle and by the row-sum property."""
+@pytest.mark.parametrize("K", [32, 64, 128])
+def test_full_size_cfg2(gpu_ctx, pkg, oracle, K):
+    """The power-law benchmark graph (R-MAT scale 20) at full size with a plan -- the kernel instantiations and
+    chunk sizes the benchmark times -- against the oracle, every element."""
     g = pkg.gen_rmat(20, 16, seed=2)
-    K = 32
-    B = pkg.host_fill_uniform(g["N"] * K, 2, 32, -1.0, 1.0).reshape(g["N"], K)
-    C, errs = _check(gpu_ctx, pkg, oracle, g["row_ptr"], g["col_idx"], g["vals"], B, "cfg2 K=32",
+    B = pkg.host_fill_uniform(g["N"] * K, 2, 100 + K, -1.0, 1.0).reshape(g["N"], K)
+    C, errs = _check(gpu_ctx, pkg, oracle, g["row_ptr"], g["col_idx"], g["vals"], B, "cfg2 K=%d" % K,
                      use_plan=True)
     deg = np.diff(g["row_ptr"])
     assert np.all(C[deg == 0] == 0)
+
+
+def test_host_entry_with_several_products(gpu_ctx, pkg, oracle):
+    """hpspmm_spmm_csr_f32_host_multi: A uploaded once, the slabs of all products through one pipeline."""
+    g = pkg.gen_rmat(12, 16, seed=6)
+    M, N, nnz = g["M"], g["N"], g["nnz"]
+    Ks = [32, 64, 128, 40, 96]
+    Bs = [pkg.host_fill_uniform(N * K, 6, K, -1.0, 1.0).reshape(N, K) for K in Ks]
+    Cs = [np.full((M, K), np.nan, dtype=np.float32) for K in Ks]
+    gpu_ctx.spmm_csr_host_multi(M, N, nnz, g["row_ptr"], g["col_idx"], g["vals"], Ks, Bs, Cs)
+    for K, B, C in zip(Ks, Bs, Cs):
+        ref, abs_sum = oracle.spmm_f64(g["row_ptr"], g["col_idx"], g["vals"], B)
+        check_against_f64(C, ref, abs_sum, "host multi K=%d" % K)
+    # no products, and an empty matrix, are fine; a bad width is refused
+    gpu_ctx.spmm_csr_host_multi(M, N, nnz, g["row_ptr"], g["col_idx"], g["vals"], [], [], [])
+    with pytest.raises(pkg.HpspmmError) as e:
+        gpu_ctx.spmm_csr_host_multi(M, N, nnz, g["row_ptr"], g["col_idx"], g["vals"], [0], [Bs[0]], [Cs[0]])
+    assert e.value.status == pkg.ERR_INVALID
 
 
 @pytest.mark.parametrize("K", [32, 64, 128, 192, 96, 40])

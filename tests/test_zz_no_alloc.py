@@ -72,4 +72,12 @@ def test_static_scratch_rejects_oversized_matrices(gpu_ctx, pkg):
     st = lib.hpspmm_spmm_csr_f32_static_scratch(0, 4, 4, 0, 0, d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, None,
                                                 err, len(err))
     assert st == pkg.ERR_INVALID and err.value
+    # a device the process does not have is refused by name, even for an empty matrix, and launches nothing
+    for M in (4, 0):
+        st = lib.hpspmm_spmm_csr_f32_static_scratch(63, M, 4, 32, 0, d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, None,
+                                                    err, len(err))
+        assert st == pkg.ERR_INVALID and b"does not exist" in err.value
+    st = lib.hpspmm_spmm_csr_f32_static_scratch(64, 4, 4, 32, 0, d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, None,
+                                                err, len(err))
+    assert st == pkg.ERR_INVALID and b"out of range" in err.value
     d.free()
