@@ -150,7 +150,7 @@ PROTOTYPES = {
     "hpspmm_sharded_exchange_begin": (c_int, [_P, _P, c_int32, _I64, _P, _P]),
     "hpspmm_sharded_product": (c_int, [_P, _P, c_int32, _I64, _P, _P, POINTER(Opts), _P]),
     "hpspmm_spmm_sharded_f32": (c_int, [_P, _P, _I64, _P, _P, _P, POINTER(Opts), _P]),
-    "hpspmm_debug_fail_device_alloc": (c_int, [_I64]),
+    "hpspmm_debug_fail_device_alloc": (c_int, [_I64, _I64]),
     "hpspmm_probe_gather_gbs": (c_int, [_P, c_int32, _I64, _I64, c_int32, _I64, c_double, c_int32,
                                         POINTER(c_double), POINTER(c_double)]),
 }

@@ -7,19 +7,18 @@
 
 #include "hpspmm_internal.h"
 
-// Allocation-failure seam for tests: > 0 counts down with every device allocation, the one that
-// reaches zero fails; 0 = disarmed.
-static std::atomic<int64_t> g_fail_alloc_countdown{0};
+// Allocation-failure seam for tests: g_fail_skip allocations still succeed, then g_fail_count fail.
+static std::atomic<int64_t> g_fail_skip{0};
+static std::atomic<int64_t> g_fail_count{0};
 
 cudaError_t hpspmm_device_malloc(void** out, size_t bytes) {
-  int64_t left = g_fail_alloc_countdown.load(std::memory_order_relaxed);
-  while (left > 0) {
-    if (g_fail_alloc_countdown.compare_exchange_weak(left, left - 1, std::memory_order_relaxed)) {
-      if (left == 1) {
-        if (out) *out = nullptr;
-        return cudaErrorMemoryAllocation;
-      }
-      break;
+  if (g_fail_count.load(std::memory_order_relaxed) > 0) {
+    if (g_fail_skip.load(std::memory_order_relaxed) > 0) {
+      g_fail_skip.fetch_sub(1, std::memory_order_relaxed);
+    } else {
+      g_fail_count.fetch_sub(1, std::memory_order_relaxed);
+      if (out) *out = nullptr;
+      return cudaErrorMemoryAllocation;
     }
   }
   return cudaMalloc(out, bytes);
@@ -27,9 +26,11 @@ cudaError_t hpspmm_device_malloc(void** out, size_t bytes) {
 
 extern "C" {
 
-int hpspmm_debug_fail_device_alloc(int64_t nth) {
-  if (nth < 0) return HPSPMM_ERR_INVALID;
-  g_fail_alloc_countdown.store(nth, std::memory_order_relaxed);
+int hpspmm_debug_fail_device_alloc(int64_t nth, int64_t count) {
+  if (nth < 0 || count < 0) return HPSPMM_ERR_INVALID;
+  g_fail_count.store(0, std::memory_order_relaxed);
+  g_fail_skip.store(nth > 0 ? nth - 1 : 0, std::memory_order_relaxed);
+  g_fail_count.store(nth > 0 ? count : 0, std::memory_order_relaxed);
   return HPSPMM_OK;
 }
 

@@ -77,8 +77,13 @@ __device__ __forceinline__ void reduce4_transposed(float (&p)[4], int lane) {
 // X and Y (row stride ld); 1 writes the partial dot products, 2 adds them to what earlier slabs wrote.
 // When a row ends the kernel steps to the next row that holds entries through the list nz_id / nz_end (chunk_ri:
 // position in that list of the row holding a chunk's first entry), so it never looks at an empty row.
+// resident 64-thread blocks per SM the kernel is compiled for: 20 (48 registers) measured 0.193 / 0.318 /
+// 0.542 ms at K = 32 / 64 / 128 on the R-MAT scale-20 graph against 0.204 / 0.318 / 0.555 ms at 18 (56 registers)
+#ifndef HPSPMM_SDDMM_MINB
+#define HPSPMM_SDDMM_MINB 20
+#endif
 template <int W, bool HINT, int BT, int SLAB>
-__global__ void __launch_bounds__(BT)
+__global__ void __launch_bounds__(BT, HPSPMM_SDDMM_MINB)
 sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
                   const int* __restrict__ col_idx, const float* __restrict__ X,
                   const float* __restrict__ Y, float* __restrict__ out,
@@ -122,25 +127,25 @@ sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
 
   float4 x = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row * K + l * 4));
   const float* Yl = Y + l * 4;
-  // The fragment of the NEXT row of X that holds entries is fetched one row ahead: a row of X is a miss to L2
-  // or DRAM, and fetched on demand its latency would be paid once per row (every 15 entries on a power-law
-  // graph's short rows) with nothing of the same warp to overlap it.  The list ends in the sentinel row M,
-  // which has no fragment.
-  int row_n = __ldg(nz_id + ri + 1);
-  int row_end_n = __ldg(nz_end + ri + 1);
-  float4 xn = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (row_n < M) xn = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row_n * K + l * 4));
-
-  // entry `next_entry` starts a later row: step to it and start fetching the one after
+  // entry `next_entry` starts a later row: find it and fetch its fragment of X
   auto next_x = [&](int next_entry) {
     (void)next_entry;   // the list of rows that hold entries names the row directly
     ++ri;
-    row = row_n;
-    row_end = row_end_n;
-    x = xn;
-    row_n = __ldg(nz_id + ri + 1);
-    row_end_n = __ldg(nz_end + ri + 1);
-    if (row_n < M) xn = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row_n * K + l * 4));
+    row = __ldg(nz_id + ri);
+    row_end = __ldg(nz_end + ri);
+    x = __ldg(reinterpret_cast<const float4*>(X + (int64_t)row * K + l * 4));
+  };
+
+  // reduce the U partial dot products of a batch over the W lanes of each group and store the U * G results
+  auto finish_batch = [&](float (&part)[U], int j0) {
+    reduce4_transposed(part, lane);
+    float total = part[0];
+    total += __shfl_xor_sync(0xffffffffu, total, 4);
+    if (W >= 16) total += __shfl_xor_sync(0xffffffffu, total, 8);
+    if (W >= 32) total += __shfl_xor_sync(0xffffffffu, total, 16);
+    const int which = ((l & 1) << 1) | ((l >> 1) & 1);   // which of the U entries lane l holds
+    const int j = j0 + which * G + g;
+    if (l < 4 && j < n1) out[j] = SLAB == 2 ? out[j] + total : total;
   };
 
   int stage = 0;
@@ -148,42 +153,49 @@ sddmm_warp_kernel(int M, int n_chunks, const int* __restrict__ row_ptr,
     cp_async_wait<STAGES - 1>();
     __syncwarp();
     const int* tile = &my[stage][g];
-#pragma unroll 1
-    for (int u0 = 0; u0 < T; u0 += BATCH) {
-      const int j0 = base + u0;
-      if (j0 >= n1) break;
-      float4 y[U];
+    if (base + T <= n1 && row_end >= base + T) {
+      // Fast tile: all 32 entries belong to the current row.  Fully unrolled, every shared-memory offset a
+      // compile-time constant, no tests between gathers (two thirds of the tiles of a power-law graph).
 #pragma unroll
-      for (int i = 0; i < U; ++i) y[i] = ld_gather<HINT>(Yl + (int64_t)tile[u0 + i * G] * K, policy);
-      float part[U];
-      if (row_end >= j0 + BATCH) {
+      for (int u0 = 0; u0 < T; u0 += BATCH) {
+        float4 y[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) y[i] = ld_gather<HINT>(Yl + (int64_t)tile[u0 + i * G] * K, policy);
+        float part[U];
 #pragma unroll
         for (int i = 0; i < U; ++i) part[i] = dot4(x, y[i], 0.f);
-      } else {
-#pragma unroll
-        for (int i = 0; i < U; ++i) {
-          const int lo = j0 + i * G;
-          const int hi = min(lo + G, n1);
-          const int mine = lo + g;
-          int cur = lo;
-          part[i] = 0.f;
-          while (row_end < hi) {   // warp-uniform: the current row ends inside this step
-            if (mine >= cur && mine < row_end) part[i] = dot4(x, y[i], 0.f);
-            cur = row_end;
-            next_x(cur);
-          }
-          if (mine >= cur) part[i] = dot4(x, y[i], 0.f);
-        }
+        finish_batch(part, base + u0);
       }
-      // reduce the U partial dot products over the W lanes of each group
-      reduce4_transposed(part, lane);
-      float total = part[0];
-      total += __shfl_xor_sync(0xffffffffu, total, 4);
-      if (W >= 16) total += __shfl_xor_sync(0xffffffffu, total, 8);
-      if (W >= 32) total += __shfl_xor_sync(0xffffffffu, total, 16);
-      const int slot = ((l & 1) << 1) | ((l >> 1) & 1);   // which of the U entries lane l holds
-      const int j = j0 + slot * G + g;
-      if (l < 4 && j < n1) out[j] = SLAB == 2 ? out[j] + total : total;
+    } else {
+#pragma unroll 1
+      for (int u0 = 0; u0 < T; u0 += BATCH) {
+        const int j0 = base + u0;
+        if (j0 >= n1) break;
+        float4 y[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) y[i] = ld_gather<HINT>(Yl + (int64_t)tile[u0 + i * G] * K, policy);
+        float part[U];
+        if (row_end >= j0 + BATCH) {
+#pragma unroll
+          for (int i = 0; i < U; ++i) part[i] = dot4(x, y[i], 0.f);
+        } else {
+#pragma unroll
+          for (int i = 0; i < U; ++i) {
+            const int lo = j0 + i * G;
+            const int hi = min(lo + G, n1);
+            const int mine = lo + g;
+            int cur = lo;
+            part[i] = 0.f;
+            while (row_end < hi) {   // warp-uniform: the current row ends inside this step
+              if (mine >= cur && mine < row_end) part[i] = dot4(x, y[i], 0.f);
+              cur = row_end;
+              next_x(cur);
+            }
+            if (mine >= cur) part[i] = dot4(x, y[i], 0.f);
+          }
+        }
+        finish_batch(part, j0);
+      }
     }
     __syncwarp();
     stage_tile(stage, base + STAGES * T);

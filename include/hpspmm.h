@@ -474,12 +474,13 @@ HPSPMM_API double hpspmm_sddmm_algorithmic_bytes(int64_t M_ref, int64_t N_ref, i
                                                  int64_t M, int64_t nnz);
 
 /* ---- diagnostics: allocation-failure seam ------------------------------------------------------------
- * Test hook: the nth device allocation the library makes from now on (1 = the next one) reports an
- * out-of-memory error without touching the device, once; 0 disarms.  Process-wide.  Lets a test see
- * that every entry point that allocates returns HPSPMM_ERR_OOM, frees what it had already taken and
- * leaves the context usable -- where the reference ignores the result of cudaMalloc altogether
+ * Test hook: starting with the nth device allocation the library makes from now on (1 = the next one),
+ * `count` allocations in a row report an out-of-memory error without touching the device; nth = 0
+ * disarms.  Process-wide, meant for single-threaded tests.  Lets a test see that every entry point
+ * that allocates returns HPSPMM_ERR_OOM, frees what it had already taken and leaves the context usable
+ * -- where the reference ignores the result of cudaMalloc altogether
  * (spmm/starml/basic/allocator_cuda.cpp:5-13). */
-HPSPMM_API int hpspmm_debug_fail_device_alloc(int64_t nth);
+HPSPMM_API int hpspmm_debug_fail_device_alloc(int64_t nth, int64_t count);
 
 /* ---- diagnostics: load-path ceilings ---------------------------------------------------------------
  * Times the gather shape of the product kernels alone (lane groups of row_bytes / 16 lanes,

@@ -3,11 +3,12 @@
 Run on a B200 (the reference is CUDA-only), after `make -C oracle ref` has built
 oracle/_ref/libref_spmm.so from the reference's sources:
 
-    python tests/golden/make_golden.py [--out DIR] [--time-bench-graph]
+    python tests/golden/make_golden.py [--out DIR] [--time-bench-graph] [--only-cfg2]
 
 For every case it stores the inputs and what the reference's GESpMM (CSR, overwrite) and
 LBSpMM (padded COO, 200 accumulating launches, divided by 200 as the reference's checker
-does) leave in C.  --time-bench-graph additionally times both reference entry points on the
+does) leave in C.  The power-law benchmark graph (R-MAT scale 20, K = 32) is stored as sampled rows plus
+column sums (cfg2_k32_sampled_rows.npz; --only-cfg2 writes that file alone).  --time-bench-graph additionally times both reference entry points on the
 benchmark graph (R-MAT scale 20) and writes the milliseconds to reference_timings.json.
 """
 import argparse
@@ -50,16 +51,52 @@ def run_ref(lib, g, B, oracle_lib):
     return C_ge, C_lb, ge_ms, ms.value
 
 
+def cfg2_sample_rows(row_ptr):
+    """The rows of the scale-20 benchmark graph that are stored: the four heaviest, 120 spread over the rows that
+    hold entries, and four empty ones."""
+    deg = np.diff(row_ptr)
+    heavy = np.argsort(deg, kind="stable")[-4:]
+    nonempty = np.flatnonzero(deg > 0)
+    spread = nonempty[np.linspace(0, len(nonempty) - 1, 120).astype(np.int64)]
+    empty = np.flatnonzero(deg == 0)[:4]
+    return np.unique(np.concatenate([heavy, spread, empty])).astype(np.int64)
+
+
+def golden_cfg2(pkg, lib, oracle_lib, out_dir):
+    """The power-law benchmark configuration at full size (R-MAT scale 20, K = 32, the benchmark's seeds):
+    inputs are regenerated from their seeds by the tests; sampled rows of both reference outputs and the
+    column sums of GESpMM's are stored."""
+    g = pkg.gen_rmat(20, 16, seed=2)
+    K = 32
+    B = pkg.host_fill_uniform(g["N"] * K, 2, 100 + K, -1.0, 1.0).reshape(g["N"], K)
+    C_ge, C_lb, ge_ms, lb_ms = run_ref(lib, g, B, oracle_lib)
+    rows = cfg2_sample_rows(g["row_ptr"])
+    np.savez_compressed(os.path.join(out_dir, "cfg2_k32_sampled_rows.npz"), rows=rows, C_gespmm=C_ge[rows],
+                        C_lbspmm_div200=C_lb[rows], col_sum_gespmm=C_ge.astype(np.float64).sum(axis=0))
+    info = {"M": g["M"], "N": g["N"], "nnz": g["nnz"], "K": K, "rows_stored": int(len(rows)),
+            "max_degree": int(np.diff(g["row_ptr"]).max()),
+            "gespmm_equals_fp32_oracle": bool(np.array_equal(
+                C_ge, oracle_lib.spmm_f32(g["row_ptr"], g["col_idx"], g["vals"], B))),
+            "gespmm_ms": ge_ms, "lbspmm_ms": lb_ms}
+    json.dump(info, open(os.path.join(out_dir, "cfg2_k32_summary.json"), "w"), indent=1)
+    return info
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=HERE)
     ap.add_argument("--time-bench-graph", action="store_true")
+    ap.add_argument("--only-cfg2", action="store_true")
     args = ap.parse_args()
     import __graft_entry__ as entry
     import oracle_lib
     pkg = entry.load_package()
     lib = load_ref()
     os.makedirs(args.out, exist_ok=True)
+
+    if args.only_cfg2:
+        print(json.dumps(golden_cfg2(pkg, lib, oracle_lib, args.out)))
+        return
 
     cases = {
         "uniform512_k32": (pkg.gen_uniform_degree(512, 512, 1, 32, seed=1, vals_kind=pkg.VALS_UPM1), 32),
@@ -103,6 +140,7 @@ def main():
                                "lbspmm_backward_err": float(np.max(np.abs(C_lb - ref) / np.maximum(abs_sum, 1e-30)))}
         json.dump(timings, open(os.path.join(args.out, "reference_timings.json"), "w"), indent=1)
         print(json.dumps(timings))
+    summary["cfg2_k32"] = golden_cfg2(pkg, lib, oracle_lib, args.out)
     json.dump(summary, open(os.path.join(args.out, "summary.json"), "w"), indent=1)
     print(json.dumps(summary))
 

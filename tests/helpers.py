@@ -2,13 +2,17 @@
 import numpy as np
 
 # Tolerances (required: max relative error 1e-4, FP32 summation-order differences only).
-# Measured over the whole GPU suite the backward error |got - ref| / sum|terms| peaks at 1.9e-7 (SpMM,
-# rows of 40 K entries summed in chunks) and 4.5e-8 (SDDMM): FP32 rounding, 6e-8 per operation, grows
-# with the logarithm of the row length when partial sums are combined pairwise.  2e-6 leaves a factor
-# of ten for other graphs and still rejects a dropped term of weight 2e-6 of its row.
-REL_TOL = 1e-4          # elementwise, on well-conditioned elements, and normwise
-BACKWARD_TOL = 2e-6     # |got - ref| / sum|terms|, every element
-WELL_CONDITIONED = 1e-3  # an element is well conditioned if |ref| >= this * sum|terms| (condition number <= 1000)
+# Measured over the whole GPU suite the backward error |got - ref| / sum|terms| peaks at 1.9e-7 (SpMM, rows
+# of 40 K entries summed in chunks) and 4.5e-8 (SDDMM): FP32 rounding, 6e-8 per operation, grows with the
+# logarithm of the row length when partial sums are combined pairwise.  BACKWARD_TOL = 2e-6 leaves a factor
+# of ten for other graphs and rejects a dropped term that weighs 2e-6 of its row or more.
+# The relative error of an element is its backward error times its condition number sum|terms| / |ref|, so a
+# relative bound only makes sense up to some condition number: with the cut at 1000 (|ref| >= 1e-3 sum|terms|)
+# the uniform-sparse full-size case (157 M elements, B in U(-1,1) cancelling) measured 1.07e-4 -- plain FP32
+# rounding already passes 1e-4 there, whatever the kernel; at 400 the same run stays under 5e-5.
+REL_TOL = 1e-4             # elementwise on well-conditioned elements, and normwise
+BACKWARD_TOL = 2e-6        # |got - ref| / sum|terms|, every element
+WELL_CONDITIONED = 2.5e-3  # an element is well conditioned if |ref| >= this * sum|terms| (condition number <= 400)
 
 
 def check_against_f64(got, ref64, abs_sum, what=""):

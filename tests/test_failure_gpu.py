@@ -13,8 +13,12 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture
 def seam(pkg):
     lib = pkg.load_library()
-    yield lib.hpspmm_debug_fail_device_alloc
-    lib.hpspmm_debug_fail_device_alloc(0)
+
+    def arm(nth, count=1):
+        return lib.hpspmm_debug_fail_device_alloc(nth, count)
+
+    yield arm
+    lib.hpspmm_debug_fail_device_alloc(0, 0)
 
 
 def _free_bytes():
@@ -55,7 +59,13 @@ def test_planless_and_host_products_report_oom_and_recover(pkg, oracle, seam):
     with pkg.Context(0) as ctx:                              # a fresh context owns no scratch yet
         d_rp, d_ci, d_v, d_B = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"]), ctx.upload(g["vals"]), ctx.upload(B)
         d_C = ctx.alloc((M, 64), np.float32)
-        seam(1)
+        seam(1)                                              # the scratch is asked for a second, smaller time ...
+        ctx.spmm_csr(M, N, 64, nnz, d_rp, d_ci, d_v, d_B, d_C)
+        check_against_f64(d_C.to_host(), ref, abs_sum, "plan-less product, second allocation attempt")
+    with pkg.Context(0) as ctx:
+        d_rp, d_ci, d_v, d_B = ctx.upload(g["row_ptr"]), ctx.upload(g["col_idx"]), ctx.upload(g["vals"]), ctx.upload(B)
+        d_C = ctx.alloc((M, 64), np.float32)
+        seam(1, 2)                                           # ... and when that fails too, the call reports it
         with pytest.raises(pkg.HpspmmError) as e:
             ctx.spmm_csr(M, N, 64, nnz, d_rp, d_ci, d_v, d_B, d_C)
         assert e.value.status == pkg.ERR_OOM
@@ -67,7 +77,7 @@ def test_planless_and_host_products_report_oom_and_recover(pkg, oracle, seam):
         with pytest.raises(pkg.HpspmmError) as e:
             ctx.spmm_csr_host(M, N, 64, nnz, g["row_ptr"], g["col_idx"], g["vals"], B, C)
         assert e.value.status == pkg.ERR_OOM
-        seam(2)                                              # ... and the kernel scratch the second
+        seam(2, 2)                                           # ... and the kernel scratch the second (two attempts)
         with pytest.raises(pkg.HpspmmError) as e:
             ctx.spmm_csr_host(M, N, 64, nnz, g["row_ptr"], g["col_idx"], g["vals"], B, C)
         assert e.value.status == pkg.ERR_OOM
@@ -108,8 +118,8 @@ def test_shard_plan_create_reports_oom(pkg, seam):
 
 
 def test_seam_argument_and_disarm(pkg, seam):
-    assert seam(-1) == pkg.ERR_INVALID
-    assert seam(3) == pkg.OK and seam(0) == pkg.OK
+    assert seam(-1) == pkg.ERR_INVALID and seam(1, -1) == pkg.ERR_INVALID
+    assert seam(3) == pkg.OK and seam(0, 0) == pkg.OK
     with pkg.Context(0) as ctx:                              # disarmed: allocations go through
         d = ctx.alloc((1024,), np.float32)
         ctx.fill(d, 1024, 2.0)
