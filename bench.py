@@ -543,11 +543,15 @@ def run_sharded(args, pkg, rank, local_rank, world):
         del full
         Cs[K] = torch.empty((M_l, K), dtype=torch.float32, device=dev)
 
+    order = list(ks)
+    slot_of = {K: i for i, K in enumerate(ks)}
+
     def step_overlapped():
-        for slot, K in enumerate(ks):
-            sp.begin(slot, K, B_own[K].data_ptr(), sptr)
-        for slot, K in enumerate(ks):
-            sp.product(slot, K, t_v.data_ptr(), Cs[K].data_ptr(), stream=sptr)
+        # narrowest first: the exchange nothing can hide is the smallest one
+        for K in order:
+            sp.begin(slot_of[K], K, B_own[K].data_ptr(), sptr)
+        for K in order:
+            sp.product(slot_of[K], K, t_v.data_ptr(), Cs[K].data_ptr(), stream=sptr)
 
     def step_kernels(events=None):
         for slot, K in enumerate(ks):
