@@ -543,11 +543,12 @@ def run_sharded(args, pkg, rank, local_rank, world):
         del full
         Cs[K] = torch.empty((M_l, K), dtype=torch.float32, device=dev)
 
-    order = list(ks)
+    order = sorted(ks, reverse=not args.narrow_first)
     slot_of = {K: i for i, K in enumerate(ks)}
 
     def step_overlapped():
-        # narrowest first: the exchange nothing can hide is the smallest one
+        # widest first: the exchanges are longer than the products, so the product left with nothing to hide
+        # behind should be the smallest one
         for K in order:
             sp.begin(slot_of[K], K, B_own[K].data_ptr(), sptr)
         for K in order:
@@ -741,6 +742,29 @@ def pkg_comm_id(pkg, dist, dev, rank):
     return bytes(idt.cpu().numpy().tobytes())
 
 
+def run_ceilings(pkg):
+    """Load-path ceilings of the GPU with the gather shape of the product kernels (hpspmm_probe_gather_gbs):
+    one JSON line with GB/s per row size and access pattern."""
+    ctx = pkg.Context(0)
+    n = 16 * 1024 * 1024
+    out = []
+    for rb in (128, 256, 512):
+        for name, rows, pattern, hot_rows, hot_share in (
+                ("stream over a 64 MB table", (64 << 20) // rb, 0, 0, 0.0),
+                ("random rows, 32 MB table (L2-resident)", (32 << 20) // rb, 1, 0, 0.0),
+                ("random rows, 64 MB table (L2-resident)", (64 << 20) // rb, 1, 0, 0.0),
+                ("random rows, 1048576-row table", 1 << 20, 1, 0, 0.0),
+                ("random rows, 546186-row table (the referenced part of B on the bench graph)", 546186, 1, 0, 0.0),
+                ("same table, 25 % of the gathers on its 1770 hottest rows", 546186, 2, 1770, 0.25),
+                ("same table, 55 % of the gathers on its 14000 hottest rows", 546186, 2, 14000, 0.55),
+                ("random rows, 4194304-row table (DRAM)", 1 << 22, 1, 0, 0.0)):
+            gbs, ms = ctx.probe_gather(rb, rows, n, pattern, hot_rows, hot_share, 10)
+            out.append({"row_bytes": rb, "pattern": name, "table_mb": rows * rb / 1e6, "ms": ms, "gbs": gbs,
+                        "bytes_per_clk_per_sm_at_1.9ghz": gbs * 1e9 / (148 * 1.9e9)})
+    ctx.close()
+    print(json.dumps({"ceilings": out, "gathers_per_launch": n}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -751,6 +775,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--only-k", type=int, default=0, help="profiling aid (one GPU): run a single K")
+    ap.add_argument("--ceilings", action="store_true",
+                    help="one GPU: measure the load-path ceilings (bare gathers) instead of the benchmark")
+    ap.add_argument("--narrow-first", action="store_true",
+                    help="N > 1: begin the exchanges in the order K = 32, 64, 128 instead of widest first")
     ap.add_argument("--no-compare", action="store_true",
                     help="skip the off-path comparison columns (cuSPARSE and the reference's kernels at N = 1, "
                          "the plain all-gather at N > 1)")
@@ -783,6 +811,10 @@ def main():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
     if world != args.gpus and world > 1:
         raise SystemExit("--gpus %d does not match WORLD_SIZE %d" % (args.gpus, world))
+    if args.ceilings:
+        if rank == 0:
+            run_ceilings(pkg)
+        return 0
     if world == 1:
         return run_single(args, pkg)
     return run_sharded(args, pkg, rank, local_rank, world)

@@ -18,6 +18,7 @@
 // atomics on this path).  Empty rows are zeroed by extra blocks at the end of the same grid.
 // HPSPMM_ALGO_ROW_SPLIT keeps the reference's GESpMM shape (one sub-warp per row, every row
 // summed in storage order), which reproduces the CPU oracle bit for bit.
+#include <algorithm>
 #include <mutex>
 #include <new>
 
@@ -1661,7 +1662,14 @@ int hpspmm_spmm_csr_f32_host_multi(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_
   for (int i = 0; i < n_products; ++i) {
     HPSPMM_REQUIRE(ctx, Ks[i] >= 1 && Ks[i] <= 512, "K must be between 1 and 512");
     HPSPMM_REQUIRE(ctx, Cs[i] != nullptr && (nnz == 0 || Bs[i] != nullptr), "null dense operand");
-    n = append_slabs(slabs, 16 * 16, n, Bs[i], Cs[i], Ks[i]);
+  }
+  // widest product first: the download of the very last slab is the one transfer nothing overlaps, so the
+  // pipeline should end on the narrowest slab
+  int order[16];
+  for (int i = 0; i < n_products; ++i) order[i] = i;
+  std::stable_sort(order, order + n_products, [&](int a, int b) { return Ks[a] > Ks[b]; });
+  for (int i = 0; i < n_products; ++i) {
+    n = append_slabs(slabs, 16 * 16, n, Bs[order[i]], Cs[order[i]], Ks[order[i]]);
     if (n < 0) return HPSPMM_ERR_UNSUPPORTED;
   }
   hpspmm_device_guard guard(ctx->device);

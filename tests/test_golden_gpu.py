@@ -54,3 +54,23 @@ def test_cfg1_against_reference_rows(gpu_ctx, pkg):
     assert np.array_equal(C[z["rows"]], z["C_gespmm"])
     C = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B)
     assert np.allclose(C[z["rows"]], z["C_gespmm"], rtol=1e-4, atol=1e-5)
+
+
+def test_cfg2_against_reference_rows(gpu_ctx, pkg, oracle):
+    """The benchmark graph at K = 32 against sampled rows of the reference's own outputs: the row-split
+    algorithm bit for bit, the balanced kernel (with the plan the benchmark uses) within the tolerance."""
+    from helpers import BACKWARD_TOL
+    z = np.load(os.path.join(GOLDEN, "cfg2_k32_sampled_rows.npz"))
+    g = pkg.gen_rmat(20, 16, seed=2)
+    B = pkg.host_fill_uniform(g["N"] * 32, 2, 132, -1.0, 1.0).reshape(g["N"], 32)
+    rows = z["rows"]
+    C = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B, opts=pkg.Opts(algo=pkg.ALGO_ROW_SPLIT))
+    assert np.array_equal(C[rows], z["C_gespmm"])
+    C = gpu_spmm(gpu_ctx, pkg, g["row_ptr"], g["col_idx"], g["vals"], B, use_plan=True)
+    sub = np.concatenate([np.arange(g["row_ptr"][r], g["row_ptr"][r + 1]) for r in rows])
+    sub_rp = np.concatenate([[0], np.cumsum(np.diff(g["row_ptr"])[rows])]).astype(np.int32)
+    _, abs_sum = oracle.spmm_f64(sub_rp, g["col_idx"][sub], g["vals"][sub], B)
+    ref = z["C_gespmm"].astype(np.float64)
+    assert np.max(np.abs(C[rows] - ref) / np.maximum(abs_sum, 1e-30)) <= BACKWARD_TOL
+    assert np.max(np.abs(C[rows] - z["C_lbspmm_div200"]) / np.maximum(abs_sum, 1e-30)) <= 1e-5
+    assert np.allclose(C.astype(np.float64).sum(axis=0), z["col_sum_gespmm"], rtol=0, atol=0.05)
