@@ -130,8 +130,10 @@ struct push_targets {
 // dst_d[first_row_d + i - list_begin_d, :] = B_own[send_rows[i], :] for every position i of the send list;
 // one 16-byte (VEC = 4) or 4-byte element per thread step, rows written whole and in order, so the
 // stores that cross NVLink are contiguous runs of K * 4 bytes.
+constexpr int kPushThreads = 64;   // the product kernels' block size: a push block fits the slot a product block leaves
+
 template <int VEC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kPushThreads)
 push_rows_kernel(const float* __restrict__ B_own, const int* __restrict__ send_rows, int64_t total_rows,
                  int64_t row_elems, push_targets t) {
   constexpr int UNROLL = 4;   // independent load -> remote store pairs in flight per thread
@@ -208,7 +210,7 @@ struct hpspmm_shard_plan {
   int32_t* d_send_rows;              // local row ids of B_own, grouped as send_off says
   cudaStream_t comm_stream;
   bool push;                         // rows travel by peer stores (else by NCCL send / receive)
-  int64_t push_blocks;               // grid of the push kernel (256-thread blocks)
+  int64_t push_blocks;               // grid of the push kernel (64-thread blocks)
   std::vector<int64_t> dst_first_row;   // world: where this rank's block starts in rank d's dense operand
   int32_t* d_token;                  // four bytes for the completion signal
   hpspmm_shard_slot slots[kSlots];
@@ -417,12 +419,15 @@ int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local
   p->d_token = nullptr;
   p->push = exchange == HPSPMM_EXCHANGE_NEEDED_ROWS && world <= kMaxPushWorld;
   p->comm_stream = nullptr;
-  // Grid of the push kernel.  Measured on two B200s (315 MB per step in the busier direction): 2 / 4 / 8 / 16
-  // blocks of 256 threads per SM move the rows in 0.72 / 0.61 / 0.54 / 0.51 ms -- remote stores need many
-  // threads in flight to fill the link -- and the step (exchange beside products) is shortest at 16.
-  // Packing locally and letting the copy engines carry the blocks (cudaMemcpyAsync to the peer mapping) was
-  // slower: 0.87 ms for the same rows, and a longer step.  HPSPMM_PUSH_BLOCKS overrides (tuning aid).
-  p->push_blocks = (int64_t)ctx->sm_count * 16;
+  // Grid of the push kernel (64-thread blocks, the product kernels' block size, so that a push block fits the slot
+  // a finished product block leaves).  Measured on two B200s (315 MB per step in the busier direction) with the
+  // same number of threads in 256-thread blocks: 2 / 4 / 8 / 16 such blocks per SM move the rows in 0.72 / 0.61 /
+  // 0.54 / 0.51 ms -- remote stores need many threads in flight to fill the link.  A smaller grid overlaps better
+  // with the product beside it (0.2 ms hidden at 2 blocks per SM against 0.07 at 16) but the step comes out the
+  // same, so the grid that finishes the exchange soonest is kept.  Packing locally and letting the copy engines
+  // carry the blocks (cudaMemcpyAsync to the peer mapping) was slower: 0.87 ms for the same rows, and a longer
+  // step.  HPSPMM_PUSH_BLOCKS overrides (tuning aid).
+  p->push_blocks = (int64_t)ctx->sm_count * 64;
   if (const char* env = getenv("HPSPMM_PUSH_BLOCKS")) {
     const long v = atol(env);
     if (v > 0) p->push_blocks = v;
@@ -639,13 +644,13 @@ int hpspmm_sharded_exchange_begin(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int32_t
       t.list_begin[world] = total_rows;
       const bool vec = (K & 3) == 0;
       const int64_t row_elems = vec ? K / 4 : K;
-      int64_t blocks = (total_rows * row_elems + 255) / 256;
+      int64_t blocks = (total_rows * row_elems + kPushThreads - 1) / kPushThreads;
       const int64_t cap = p->push_blocks;
       if (blocks > cap) blocks = cap;
       if (vec)
-        push_rows_kernel<4><<<(unsigned)blocks, 256, 0, cs>>>(B_own, p->d_send_rows, total_rows, row_elems, t);
+        push_rows_kernel<4><<<(unsigned)blocks, kPushThreads, 0, cs>>>(B_own, p->d_send_rows, total_rows, row_elems, t);
       else
-        push_rows_kernel<1><<<(unsigned)blocks, 256, 0, cs>>>(B_own, p->d_send_rows, total_rows, row_elems, t);
+        push_rows_kernel<1><<<(unsigned)blocks, kPushThreads, 0, cs>>>(B_own, p->d_send_rows, total_rows, row_elems, t);
       ctx->launches++;
       HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
     }
