@@ -426,7 +426,10 @@ int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local
   // with the product beside it (0.2 ms hidden at 2 blocks per SM against 0.07 at 16) but the step comes out the
   // same, so the grid that finishes the exchange soonest is kept.  Packing locally and letting the copy engines
   // carry the blocks (cudaMemcpyAsync to the peer mapping) was slower: 0.87 ms for the same rows, and a longer
-  // step.  HPSPMM_PUSH_BLOCKS overrides (tuning aid).
+  // step.  So was a variant that gathers tiles of rows into shared memory (cp.async) and hands each tile to the
+  // bulk-copy engine as one 16 KB store to the peer mapping (cp.async.bulk shared -> global), meant to fill the
+  // link from two small blocks per SM: 0.88 ms at two blocks per SM, 0.68 ms at four -- a bulk store to a peer
+  // completes too slowly for so few of them in flight.  HPSPMM_PUSH_BLOCKS overrides (tuning aid).
   p->push_blocks = (int64_t)ctx->sm_count * 64;
   if (const char* env = getenv("HPSPMM_PUSH_BLOCKS")) {
     const long v = atol(env);

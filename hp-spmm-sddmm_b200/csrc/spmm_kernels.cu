@@ -13,9 +13,12 @@
 // uniform).  Gathers are issued U steps at a time before the first FMA.  When a row
 // ends, the groups' partial sums are combined with shuffles and the row is stored once,
 // by plain stores.  A chunk that ends inside a heavy row hands its partial sum on through
-// a carry slot; a second, small kernel adds the carries of each split row, in chunk order,
-// to the row the owner stored -- so results are bit-reproducible from run to run (no
-// atomics on this path).  Empty rows are zeroed by extra blocks at the end of the same grid.
+// a carry slot, and the carries of a split row are added, in chunk order, to the row its last
+// piece stored.  Who adds them depends on the width: at 32 columns a second, small kernel; at 64
+// and 128 columns the pieces themselves -- each bumps a per-row counter (one atomicAdd) when its
+// part is visible, and the piece that finds the counter complete sums the carries.  Either way
+// the order of the additions is fixed by the chunking, so results are bit-reproducible from run
+// to run.  Empty rows are zeroed by extra blocks at the end of the same grid.
 // HPSPMM_ALGO_ROW_SPLIT keeps the reference's GESpMM shape (one sub-warp per row, every row
 // summed in storage order), which reproduces the CPU oracle bit for bit.
 #include <algorithm>

@@ -1,12 +1,14 @@
 // Bench driver: successor of the reference's test/test_all.cpp (lines 27-109).
 //
-//   test_all <graph> <K> [timed_launches]
+//   test_all <graph> <K> [timed_launches] [--force]
 //
 // <graph> is a .smtx file (the reference's dataset format) or one of the seeded synthetic
 // specs  cfg1 | rmat:<scale>[:<edge_factor>[:<seed>]] | er:<rows>:<mean_degree>[:<seed>] .
 // Runs the row-split (GE-SpMM shaped) kernel, the nnz-balanced kernel, the COO entry and the
 // SDDMM, checks each against a CPU CSR loop when the graph is small, and appends one CSV row to
-// ./full_graph_res.csv in the reference's layout (spmm/mm/spmm_common.cpp:34-42).
+// ./full_graph_res.csv in the reference's layout (spmm/mm/spmm_common.cpp:34-42).  A (graph, K) pair
+// that already has a row there is skipped, so a sweep that was interrupted resumes where it stopped;
+// --force measures it again.
 #include <cstdio>
 #include <cstdlib>
 #include <sstream>
@@ -44,13 +46,25 @@ static void cpu_csr_spmm(const CSR_Matrix& A, const Matrix& B, Matrix& C) {
 
 int main(int argc, char** argv) {
   if (argc < 3) {
-    std::fprintf(stderr, "usage: %s <graph.smtx | cfg1 | rmat:S[:EF[:seed]] | er:M:deg[:seed]> <K> [launches]\n", argv[0]);
+    std::fprintf(stderr, "usage: %s <graph.smtx | cfg1 | rmat:S[:EF[:seed]] | er:M:deg[:seed]> <K> [launches] [--force]\n", argv[0]);
     return 2;
   }
   try {
     const std::string spec = argv[1];
     const long long k = std::atoll(argv[2]);
-    const int launches = argc > 3 ? std::atoi(argv[3]) : EXE_NUM_CUDA;
+    bool force = false;
+    int launches = EXE_NUM_CUDA;
+    for (int a = 3; a < argc; ++a) {
+      if (std::string(argv[a]) == "--force")
+        force = true;
+      else
+        launches = std::atoi(argv[a]);
+    }
+    if (!force && result_row_present("./full_graph_res.csv", spec, k)) {
+      std::cout << spec << " at k = " << k << " is already in ./full_graph_res.csv: skipped (--force measures it again)"
+                << std::endl;
+      return 0;
+    }
     ResInfo info;
     info.filename_ = spec;
     long long num = 0, dim = 0, real_nnz = 0;

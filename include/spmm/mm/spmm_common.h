@@ -5,6 +5,7 @@
 #pragma once
 #include <cmath>
 #include <fstream>
+#include <sstream>
 #include <iostream>
 #include <string>
 #include <vector>
@@ -175,6 +176,22 @@ inline double get_standard_CV(const CSR_Matrix& h_csr) {
 
 // Appends one CSV row: file,M,N,nnz,K,rowlenCV, then label,ms,GFLOPS triples
 // (reference: spmm/mm/spmm_common.cpp:22-44; GFLOPS = 2*nnz*K/ms/1e6 with the unpadded nnz).
+// True when `filename` already holds a row for this graph and dense width (columns 1 and 5 of the layout
+// below).  The reference's harness appends blindly (spmm/mm/spmm_common.cpp:33), so a sweep restarted after a
+// failure measures everything again; a driver can ask first and skip what is there.
+inline bool result_row_present(const std::string& filename, const std::string& graph, long long dense_dim) {
+  std::ifstream f(filename);
+  std::string line;
+  while (std::getline(f, line)) {
+    std::vector<std::string> col;
+    std::stringstream ss(line);
+    std::string item;
+    while (std::getline(ss, item, ',')) col.push_back(item);
+    if (col.size() > 4 && col[0] == graph && std::atoll(col[4].c_str()) == dense_dim) return true;
+  }
+  return false;
+}
+
 inline void write_info_to_file(const std::string& filename, ResInfo& info) {
   auto tp = [&](float ms) { return ms > 0.f ? (float)hpspmm_gflops(info.num_nnz_, info.dense_dim_, ms) : 0.f; };
   info.spmm_ge_throughput_ = tp(info.spmm_ge_time_);

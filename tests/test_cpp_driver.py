@@ -23,6 +23,29 @@ def test_headers_and_driver_compile():
     assert res.returncode == 2 and "usage" in res.stderr
 
 
+def test_driver_resumes_a_sweep(tmp_path):
+    """A (graph, K) pair that already has a row in the CSV is skipped before any GPU work (no GPU needed)."""
+    path = _builder().build_test_all()
+    (tmp_path / "full_graph_res.csv").write_text(
+        "rmat:12,4096,4096,60000,64,3.1,GE-SpMM: ,0.1,1,HP-SpMM ,0.1,1,HP-SpMM(COO): ,0.1,1,HP-SDDMM: ,0.1,1,"
+        "CPU CSR loop: ,1,1\n")
+    res = subprocess.run([path, "rmat:12", "64", "5"], cwd=tmp_path, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                         text=True, timeout=60)
+    assert res.returncode == 0 and "skipped" in res.stdout
+    assert len((tmp_path / "full_graph_res.csv").read_text().splitlines()) == 1
+
+
+@pytest.mark.gpu
+def test_driver_force_and_other_widths_are_measured(tmp_path):
+    path = _builder().build_test_all()
+    for args, rows in ((["rmat:10", "32", "3"], 1), (["rmat:10", "32", "3"], 1), (["rmat:10", "64", "3"], 2),
+                       (["rmat:10", "32", "3", "--force"], 3)):
+        res = subprocess.run([path] + args, cwd=tmp_path, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                             timeout=300)
+        assert res.returncode == 0, res.stdout
+        assert len((tmp_path / "full_graph_res.csv").read_text().splitlines()) == rows
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("spec,K", [("cfg1", 32), ("rmat:12", 64), ("rmat:10", 128)])
 def test_driver_runs_and_checks_itself(tmp_path, spec, K):

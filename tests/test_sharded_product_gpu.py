@@ -29,13 +29,13 @@ def test_world_one_matches_plain_product(gpu_ctx, pkg, oracle, exchange):
     g = pkg.gen_rmat(13, 16, seed=41)          # heavy rows, 40 % empty rows, unreferenced columns
     M, N, nnz = g["M"], g["N"], g["nnz"]
     bounds, lo, hi, rp, ci, v = _shard(pkg, g, 1, 0)
-    sp = pkg.ShardedSpmm(ctx, 1, 0, None, M, N, rp, ci, bounds, 128, exchange=exchange)
+    sp = pkg.ShardedSpmm(ctx, 1, 0, None, M, N, rp, ci, bounds, 516, exchange=exchange)
     info = sp.info()
     assert info["rows_received"] == 0 and info["rows_sent"] == 0
     assert info["rows_local"] == (len(np.unique(ci)) if exchange != 1 else N)
     d_v = ctx.upload(v)
     d_rp, d_ci = ctx.upload(rp), ctx.upload(ci)
-    for K in (32, 64, 128, 20):
+    for K in (32, 64, 128, 20, 7, 516):          # 7: no 16-byte rows; 516: rows of 2064 bytes
         B = pkg.host_fill_uniform(N * K, 41, K, -1.0, 1.0).reshape(N, K)
         d_B = ctx.upload(B)
         d_C, d_C2 = ctx.alloc((M, K), np.float32), ctx.alloc((M, K), np.float32)
