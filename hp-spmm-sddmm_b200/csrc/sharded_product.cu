@@ -233,13 +233,32 @@ int nccl_fail(hpspmm_ctx* ctx, const nccl_api* api, const char* what, int rc) {
 // position of destination d in the send order (others ascending, self last)
 inline int send_slot_of(int d, int rank, int world) { return d == rank ? world - 1 : (d < rank ? d : d - 1); }
 
-void release_slot_buffers(hpspmm_ctx* ctx, hpspmm_shard_plan* p, hpspmm_shard_slot& s) {
-  for (int b = 0; b < 2; ++b) {
+// Unmaps the other ranks' buffers of a slot; true if there was anything to unmap.
+bool close_peer_mappings(hpspmm_shard_slot& s) {
+  bool any = false;
+  for (int b = 0; b < 2; ++b)
     for (int d = 0; d < kMaxPushWorld; ++d)
       if (s.peer[b][d]) {
         cudaIpcCloseMemHandle(s.peer[b][d]);
         s.peer[b][d] = nullptr;
+        any = true;
       }
+  return any;
+}
+
+// All ranks meet here (the four-byte all-reduce, waited for on the host).  An exported buffer must not be freed
+// while another process still has it mapped, so buffers are released in two steps: every rank unmaps what it
+// had mapped, the ranks meet, and only then does each free its own.
+void meet_all_ranks(hpspmm_shard_plan* p) {
+  if (p->world <= 1 || !p->comm || !p->comm->comm || !p->d_token || !p->comm_stream) return;
+  const nccl_api* api = p->comm->api;
+  if (api->AllReduce(p->d_token, p->d_token + 1, 1, kNcclInt32, kNcclSum, p->comm->comm, p->comm_stream) == 0)
+    cudaStreamSynchronize(p->comm_stream);
+}
+
+void release_slot_buffers(hpspmm_ctx* ctx, hpspmm_shard_plan* p, hpspmm_shard_slot& s) {
+  if (close_peer_mappings(s)) meet_all_ranks(p);
+  for (int b = 0; b < 2; ++b) {
     if (s.B_local[b]) cudaFree(s.B_local[b]);
     s.B_local[b] = nullptr;
   }
@@ -248,7 +267,6 @@ void release_slot_buffers(hpspmm_ctx* ctx, hpspmm_shard_plan* p, hpspmm_shard_sl
   if (s.plan) hpspmm_plan_destroy(ctx, s.plan);
   s.plan = nullptr;
   s.K_cap = 0;
-  (void)p;
 }
 
 // First use of a slot at this width (or a wider one): allocate the operand buffers, build the chunk table and,
@@ -584,6 +602,10 @@ int hpspmm_shard_plan_destroy(hpspmm_ctx* ctx, hpspmm_shard_plan* p) {
   if (!p) return HPSPMM_OK;
   hpspmm_device_guard guard(p->device);
   cudaDeviceSynchronize();
+  // unmap everything first, meet once, then free (see meet_all_ranks)
+  bool any = false;
+  for (int i = 0; i < kSlots; ++i) any = close_peer_mappings(p->slots[i]) || any;
+  if (any) meet_all_ranks(p);
   for (int i = 0; i < kSlots; ++i) {
     hpspmm_shard_slot& s = p->slots[i];
     release_slot_buffers(ctx, p, s);

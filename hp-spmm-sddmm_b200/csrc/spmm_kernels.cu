@@ -1666,11 +1666,21 @@ int hpspmm_spmm_csr_f32_host_multi(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_
     HPSPMM_REQUIRE(ctx, Ks[i] >= 1 && Ks[i] <= 512, "K must be between 1 and 512");
     HPSPMM_REQUIRE(ctx, Cs[i] != nullptr && (nnz == 0 || Bs[i] != nullptr), "null dense operand");
   }
-  // widest product first: the download of the very last slab is the one transfer nothing overlaps, so the
-  // pipeline should end on the narrowest slab
+  // Order of the products.  Downloads can start only after the first slab has been uploaded and multiplied, and the
+  // download of the very last slab overlaps nothing, so the pipeline should begin AND end on a narrow slab: the
+  // product with the narrowest slabs goes last, the next narrowest first, the others between them, widest first.
+  auto slab_width = [&](int i) { return Ks[i] % 32 != 0 ? Ks[i] : ((Ks[i] % 64 == 0 && Ks[i] >= 128) ? (int64_t)64 : (int64_t)32); };
   int order[16];
   for (int i = 0; i < n_products; ++i) order[i] = i;
-  std::stable_sort(order, order + n_products, [&](int a, int b) { return Ks[a] > Ks[b]; });
+  std::stable_sort(order, order + n_products, [&](int a, int b) {
+    return slab_width(a) != slab_width(b) ? slab_width(a) > slab_width(b) : Ks[a] > Ks[b];
+  });
+  if (n_products >= 3) {
+    // order is now widest .. narrowest; bring the second narrowest to the front
+    const int second = order[n_products - 2];
+    for (int i = n_products - 2; i > 0; --i) order[i] = order[i - 1];
+    order[0] = second;
+  }
   for (int i = 0; i < n_products; ++i) {
     n = append_slabs(slabs, 16 * 16, n, Bs[order[i]], Cs[order[i]], Ks[order[i]]);
     if (n < 0) return HPSPMM_ERR_UNSUPPORTED;

@@ -427,6 +427,8 @@ HPSPMM_API int hpspmm_shard_needed_rows(int64_t nnz_local, const int32_t* col_id
  *   them in turn, and each exchange overlaps the previous product.  All ranks must issue their begins
  *   in the same order.  The first use of a slot (or a wider K on it) allocates and synchronises.
  * hpspmm_spmm_sharded_f32 = exchange_begin + product on slot 0.
+ * destroy: collective when world > 1 and a slot was used (the ranks unmap each other's buffers, meet, then
+ *   free their own); call it once the last product has completed on this rank, before hpspmm_comm_destroy.
  * vals: the shard's values (device, nnz_local); B_own: rows_own x K (device); C_local: M_local x K.
  * No kernel reads another GPU's memory and nothing waits on the device: ordering is by stream events. */
 typedef struct hpspmm_comm hpspmm_comm;
