@@ -256,6 +256,21 @@ void meet_all_ranks(hpspmm_shard_plan* p) {
     cudaStreamSynchronize(p->comm_stream);
 }
 
+// Collective: true on every rank iff `ok` was true on every rank.  Used in set-up paths so that a failure on
+// one rank (an allocation, a mapping) makes all ranks return an error instead of leaving the others inside a
+// collective the failed rank never joins.
+bool all_ranks_ok(hpspmm_shard_plan* p, bool ok, cudaStream_t stream) {
+  if (p->world <= 1 || !p->comm || !p->comm->comm || !p->d_token) return ok;
+  const nccl_api* api = p->comm->api;
+  int32_t bad = ok ? 0 : 1, total = 1;
+  int32_t* cell = p->d_token + 8;
+  if (cudaMemcpyAsync(cell, &bad, 4, cudaMemcpyHostToDevice, stream) != cudaSuccess) return false;
+  if (api->AllReduce(cell, cell + 1, 1, kNcclInt32, kNcclSum, p->comm->comm, stream) != 0) return false;
+  if (cudaMemcpyAsync(&total, cell + 1, 4, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return false;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return false;
+  return total == 0;
+}
+
 void release_slot_buffers(hpspmm_ctx* ctx, hpspmm_shard_plan* p, hpspmm_shard_slot& s) {
   if (close_peer_mappings(s)) meet_all_ranks(p);
   for (int b = 0; b < 2; ++b) {
@@ -279,19 +294,28 @@ int ensure_slot(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int slot, int64_t K, cuda
   const int world = p->world, rank = p->rank;
   const int n_buf = p->push ? 2 : 1;
   const size_t b_loc = align_up((size_t)std::max<int64_t>(p->n_needed, 1) * (size_t)K * 4, 256);
-  for (int b = 0; b < n_buf; ++b) {
-    HPSPMM_CUDA_TRY(ctx, hpspmm_device_malloc((void**)&s.B_local[b], b_loc));
-    p->device_bytes += b_loc;
+  cudaError_t ea = cudaSuccess;
+  for (int b = 0; b < n_buf && ea == cudaSuccess; ++b) {
+    ea = hpspmm_device_malloc((void**)&s.B_local[b], b_loc);
+    if (ea == cudaSuccess) p->device_bytes += b_loc;
   }
-  if (!p->push) {
+  if (!p->push && ea == cudaSuccess) {
     const size_t b_send = align_up((size_t)std::max<int64_t>(p->send_remote, 1) * (size_t)K * 4, 256);
-    HPSPMM_CUDA_TRY(ctx, hpspmm_device_malloc((void**)&s.send_buf, b_send));
-    p->device_bytes += b_send;
+    ea = hpspmm_device_malloc((void**)&s.send_buf, b_send);
+    if (ea == cudaSuccess) p->device_bytes += b_send;
   }
-  if (!s.ev_in) {
-    HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.ev_in, cudaEventDisableTiming));
-    HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.ev_landed, cudaEventDisableTiming));
-    HPSPMM_CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.ev_read, cudaEventDisableTiming));
+  if (ea == cudaSuccess && !s.ev_in) {
+    ea = cudaEventCreateWithFlags(&s.ev_in, cudaEventDisableTiming);
+    if (ea == cudaSuccess) ea = cudaEventCreateWithFlags(&s.ev_landed, cudaEventDisableTiming);
+    if (ea == cudaSuccess) ea = cudaEventCreateWithFlags(&s.ev_read, cudaEventDisableTiming);
+  }
+  // every rank learns whether every rank got its buffers before any of them enters the handle exchange
+  if (!all_ranks_ok(p, ea == cudaSuccess, user_stream)) {
+    release_slot_buffers(ctx, p, s);
+    if (ea != cudaSuccess)
+      return hpspmm_set_err(ctx, ea == cudaErrorMemoryAllocation ? HPSPMM_ERR_OOM : HPSPMM_ERR_CUDA, "slot buffers", ea);
+    snprintf(ctx->err, sizeof(ctx->err), "another rank could not allocate its slot buffers");
+    return HPSPMM_ERR_OOM;
   }
   if (p->push && world > 1) {
     // every rank publishes the handles of its two buffers; all ranks map all of them
@@ -314,16 +338,23 @@ int ensure_slot(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int slot, int64_t K, cuda
     cudaFree(d_h);
     if (rc != 0) return nccl_fail(ctx, api, "ncclAllGather(buffer handles)", rc);
     if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "buffer handle exchange", e);
-    for (int d = 0; d < world; ++d) {
+    for (int d = 0; d < world && e == cudaSuccess; ++d) {
       if (d == rank) continue;
-      for (int b = 0; b < 2; ++b) {
+      for (int b = 0; b < 2 && e == cudaSuccess; ++b) {
         cudaIpcMemHandle_t h;
         memcpy(&h, all.data() + ((size_t)d * 2 + b) * hb, hb);
         void* ptr = nullptr;
         e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
-        if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "cudaIpcOpenMemHandle(peer operand)", e);
-        s.peer[b][d] = (float*)ptr;
+        if (e == cudaSuccess) s.peer[b][d] = (float*)ptr;
       }
+    }
+    if (!all_ranks_ok(p, e == cudaSuccess, user_stream)) {
+      close_peer_mappings(s);   // whatever this rank had mapped; then every rank meets before anybody frees
+      meet_all_ranks(p);
+      release_slot_buffers(ctx, p, s);
+      if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "cudaIpcOpenMemHandle(peer operand)", e);
+      snprintf(ctx->err, sizeof(ctx->err), "another rank could not map the peer buffers");
+      return HPSPMM_ERR_CUDA;
     }
   }
   int st = hpspmm_plan_create(ctx, p->M_local, p->n_needed, p->nnz_local, p->d_row_ptr, p->d_col, K, nullptr,
