@@ -288,7 +288,8 @@ void release_slot_buffers(hpspmm_ctx* ctx, hpspmm_shard_plan* p, hpspmm_shard_sl
 // for the push transport, map every other rank's buffers.  Collective when world > 1; synchronises.
 int ensure_slot(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int slot, int64_t K, cudaStream_t user_stream) {
   hpspmm_shard_slot& s = p->slots[slot];
-  if (s.K_cap >= K && s.plan != nullptr) return HPSPMM_OK;
+  // (a plan that has fallen back to the NCCL transport rebuilds the slots that were set up for the push)
+  if (s.K_cap >= K && s.plan != nullptr && (p->push || s.send_buf != nullptr || p->world == 1)) return HPSPMM_OK;
   HPSPMM_CUDA_TRY(ctx, cudaDeviceSynchronize());
   release_slot_buffers(ctx, p, s);
   const int world = p->world, rank = p->rank;
@@ -348,13 +349,19 @@ int ensure_slot(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int slot, int64_t K, cuda
         if (e == cudaSuccess) s.peer[b][d] = (float*)ptr;
       }
     }
+    // test seam: HPSPMM_DEBUG_FAIL_PEER_MAPPING=<rank> makes that rank behave as if a mapping had failed
+    if (const char* env = getenv("HPSPMM_DEBUG_FAIL_PEER_MAPPING"))
+      if (atoi(env) == rank && e == cudaSuccess) e = cudaErrorInvalidDevice;
     if (!all_ranks_ok(p, e == cudaSuccess, user_stream)) {
+      // Some rank cannot map a peer's buffer (no peer access between two of the devices, IPC not permitted in
+      // this process ...).  Every rank has just learnt it, so all of them fall back together to the transport that
+      // needs no mapping: the same rows, packed and sent with ncclSend / ncclRecv.
       close_peer_mappings(s);   // whatever this rank had mapped; then every rank meets before anybody frees
       meet_all_ranks(p);
       release_slot_buffers(ctx, p, s);
-      if (e != cudaSuccess) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "cudaIpcOpenMemHandle(peer operand)", e);
-      snprintf(ctx->err, sizeof(ctx->err), "another rank could not map the peer buffers");
-      return HPSPMM_ERR_CUDA;
+      if (e != cudaSuccess) cudaGetLastError();   // the failed mapping is not an error of this call
+      p->push = false;
+      return ensure_slot(ctx, p, slot, K, user_stream);
     }
   }
   int st = hpspmm_plan_create(ctx, p->M_local, p->n_needed, p->nnz_local, p->d_row_ptr, p->d_col, K, nullptr,

@@ -106,6 +106,9 @@ def test_plan_argument_errors(gpu_ctx, pkg):
 def _rank_main(rank, world, exchange, out_dir):
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    if exchange == 10:      # the push transport with one rank unable to map its peer's buffers: all fall back to NCCL
+        os.environ["HPSPMM_DEBUG_FAIL_PEER_MAPPING"] = "1"
+        exchange = 0
     import __graft_entry__ as entry
     pkg = entry.load_package()
     id_path = os.path.join(out_dir, "comm_id.bin")
@@ -149,7 +152,7 @@ def _rank_main(rank, world, exchange, out_dir):
     ctx.close()
 
 
-@pytest.mark.parametrize("exchange", [0, 1, 2])
+@pytest.mark.parametrize("exchange", [0, 1, 2, 10])
 def test_two_gpu_exchange_and_product(tmp_path, pkg, oracle, exchange):
     import torch
     if torch.cuda.device_count() < 2:
