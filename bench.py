@@ -142,8 +142,8 @@ def workload_name(n_gpus):
     base = "rmat scale %d ef %d symmetric, K=%s" % (SCALE, EDGE_FACTOR, "/".join(map(str, KS)))
     if n_gpus == 1:
         return base + ", operands resident, C = A*B"
-    return base + (", strong-scaled over %d nnz-balanced row blocks; B row-sharded like A, needed rows "
-                   "exchanged over NCCL inside the step; C row-sharded" % n_gpus)
+    return base + (", strong-scaled over %d row blocks balanced by entries + a weight per row; B row-sharded like A, "
+                   "the rows each shard references exchanged inside the step; C row-sharded" % n_gpus)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -515,7 +515,8 @@ def run_sharded(args, pkg, rank, local_rank, world):
     g = pkg.gen_rmat(SCALE, EDGE_FACTOR, seed=GRAPH_SEED)     # every rank builds the same seeded graph
     info = graph_info(g)
     N, nnz_total = g["N"], g["nnz"]
-    bounds = pkg.shard_bounds(g["row_ptr"], world)
+    bounds = (pkg.shard_bounds_weighted(g["row_ptr"], world, args.row_weight) if args.row_weight > 0
+              else pkg.shard_bounds(g["row_ptr"], world))
     lo, hi = int(bounds[rank]), int(bounds[rank + 1])
     rp, ci, v = pkg.shard_csr(g["row_ptr"], g["col_idx"], g["vals"], lo, hi)
     rp, ci, v = (np.ascontiguousarray(a) for a in (rp, ci, v))
@@ -700,6 +701,7 @@ def run_sharded(args, pkg, rank, local_rank, world):
                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                     "algorithmic_bytes": alg[Kd], "ms": per_k_ms[Kd]}
         cfg = {"workload": workload_name(world), "parallelism": "row-shard x%d" % world,
+               "row_weight": args.row_weight, "row_bounds": [int(x) for x in bounds],
                "b": "row-sharded; per product each rank receives the rows its shard references, pushed by their owners "
                     "into its own HBM (peer stores over NVLink, a 4-byte NCCL all-reduce as the completion signal); "
                     "three exchanges begun first, products in turn",
@@ -856,6 +858,10 @@ def main():
                          "replicated (a secondary measurement, kernel time only)")
     ap.add_argument("--ceilings", action="store_true",
                     help="one GPU: measure the load-path ceilings (bare gathers) instead of the benchmark")
+    ap.add_argument("--row-weight", type=float, default=8.0,
+                    help="N > 1: cut the row blocks by entries + ROW_WEIGHT per row (0 = by entries alone).  A block of "
+                         "many short rows owns more vertices, hence sends more rows of B; on the benchmark graph the "
+                         "step is shortest around 8 to 12")
     ap.add_argument("--narrow-first", action="store_true",
                     help="N > 1: begin the exchanges in the order K = 32, 64, 128 instead of widest first")
     ap.add_argument("--no-compare", action="store_true",

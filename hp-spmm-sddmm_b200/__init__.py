@@ -134,6 +134,7 @@ PROTOTYPES = {
     "hpspmm_gen_free": (c_int, [_P]),
     "hpspmm_read_smtx": (c_int, [c_char_p, POINTER(_P)]),
     "hpspmm_shard_bounds": (c_int, [_I64, _P, c_int32, _P]),
+    "hpspmm_shard_bounds_weighted": (c_int, [_I64, _P, c_int32, c_double, _P]),
     "hpspmm_shard_row_ptr": (c_int, [_P, _I64, _I64, _P, POINTER(_I64), POINTER(_I64)]),
     "hpspmm_gflops": (c_double, [_I64, _I64, c_double]),
     "hpspmm_row_length_cv": (c_double, [_I64, _P]),
@@ -543,6 +544,16 @@ def shard_bounds(row_ptr, G):
     out = np.empty(G + 1, dtype=np.int64)
     _gen_check(lib, lib.hpspmm_shard_bounds(len(row_ptr) - 1, row_ptr.ctypes.data, G, out.ctypes.data),
                "hpspmm_shard_bounds")
+    return out
+
+
+def shard_bounds_weighted(row_ptr, G, row_weight):
+    """Row blocks balanced by entries + row_weight per row (hpspmm_shard_bounds_weighted)."""
+    lib = load_library()
+    row_ptr = np.ascontiguousarray(row_ptr, dtype=np.int32)
+    out = np.empty(G + 1, dtype=np.int64)
+    _gen_check(lib, lib.hpspmm_shard_bounds_weighted(len(row_ptr) - 1, row_ptr.ctypes.data, G, float(row_weight),
+                                                     out.ctypes.data), "hpspmm_shard_bounds_weighted")
     return out
 
 

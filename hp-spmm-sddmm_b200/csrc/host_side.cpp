@@ -368,6 +368,28 @@ int hpspmm_shard_bounds(int64_t M, const int32_t* row_ptr_host, int32_t G, int64
   return HPSPMM_OK;
 }
 
+int hpspmm_shard_bounds_weighted(int64_t M, const int32_t* row_ptr_host, int32_t G, double row_weight,
+                                 int64_t* bounds) {
+  if (M < 0 || !row_ptr_host || G < 1 || !bounds || !(row_weight >= 0.0)) return HPSPMM_ERR_INVALID;
+  // cost of rows [0, r): their entries plus row_weight per row; monotone in r, so every cut is a binary search
+  const double total = (double)row_ptr_host[M] + row_weight * (double)M;
+  bounds[0] = 0;
+  for (int32_t g = 1; g < G; ++g) {
+    const double target = total * (double)g / (double)G;
+    int64_t lo = 0, hi = M;
+    while (lo < hi) {
+      const int64_t mid = (lo + hi) >> 1;
+      if ((double)row_ptr_host[mid] + row_weight * (double)mid < target)
+        lo = mid + 1;
+      else
+        hi = mid;
+    }
+    bounds[g] = lo < bounds[g - 1] ? bounds[g - 1] : lo;
+  }
+  bounds[G] = M;
+  return HPSPMM_OK;
+}
+
 int hpspmm_shard_row_ptr(const int32_t* row_ptr_host, int64_t row_lo, int64_t row_hi,
                          int32_t* local_row_ptr, int64_t* nnz_lo_out, int64_t* nnz_local_out) {
   if (!row_ptr_host || !local_row_ptr || row_lo < 0 || row_hi < row_lo) return HPSPMM_ERR_INVALID;

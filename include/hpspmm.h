@@ -386,6 +386,13 @@ HPSPMM_API int hpspmm_read_row_order(const char* path, int64_t M, int32_t* order
  * single-GPU; this has no counterpart there. */
 HPSPMM_API int hpspmm_shard_bounds(int64_t M, const int32_t* row_ptr_host, int32_t G,
                                    int64_t* bounds);
+/* The same cut with a cost per row added to the entries: bounds[g] = first row r with
+ * row_ptr[r] + row_weight * r >= g * (nnz + row_weight * M) / G.  A block of many short rows writes more
+ * of C and ends more rows than a block of few heavy rows with the same entries; on the power-law
+ * benchmark graph a product costs about as much per row as per two to three entries.  row_weight = 0 gives
+ * hpspmm_shard_bounds. */
+HPSPMM_API int hpspmm_shard_bounds_weighted(int64_t M, const int32_t* row_ptr_host, int32_t G,
+                                            double row_weight, int64_t* bounds);
 /* Local row_ptr of shard [row_lo, row_hi): local_row_ptr[i] = row_ptr[row_lo+i] - row_ptr[row_lo],
  * row_hi-row_lo+1 entries; *nnz_lo_out / *nnz_local_out give the slice of col_idx / vals. */
 HPSPMM_API int hpspmm_shard_row_ptr(const int32_t* row_ptr_host, int64_t row_lo, int64_t row_hi,

@@ -155,6 +155,24 @@ def test_shards_tile_the_matrix_for_every_world_size(pkg, oracle):
         assert sizes.max() - sizes.min() <= 2 * np.diff(g["row_ptr"]).max()
 
 
+def test_weighted_bounds(pkg):
+    g = pkg.gen_rmat(12, 16, seed=27)
+    rp, M = g["row_ptr"], g["M"]
+    for G in (1, 2, 3, 8):
+        assert np.array_equal(pkg.shard_bounds_weighted(rp, G, 0.0), pkg.shard_bounds(rp, G))
+        for w in (0.5, 2.0, 16.0):
+            b = pkg.shard_bounds_weighted(rp, G, w)
+            assert b[0] == 0 and b[-1] == M and np.all(np.diff(b) >= 0)
+            cost = rp[b].astype(np.float64) + w * b
+            parts = np.diff(cost)
+            # every block within one row's cost of the ideal share
+            assert np.all(np.abs(parts - cost[-1] / G) <= np.diff(rp).max() + w + 1)
+    # a heavier row weight moves the first cut (the hub rows come first in an R-MAT graph) to later rows
+    assert pkg.shard_bounds_weighted(rp, 2, 8.0)[1] > pkg.shard_bounds(rp, 2)[1]
+    with pytest.raises(pkg.HpspmmError):
+        pkg.shard_bounds_weighted(rp, 2, -1.0)
+
+
 def test_degenerate_shards(pkg):
     rp = np.array([0, 0, 0, 5, 5], dtype=np.int32)      # one non-empty row, four shards
     b = pkg.shard_bounds(rp, 4)
