@@ -420,24 +420,28 @@ HPSPMM_API int hpspmm_shard_needed_rows(int64_t nnz_local, const int32_t* col_id
  * comm: a communicator over NCCL (looked up at run time with dlopen; NCCL is needed only when
  *   world > 1).  hpspmm_comm_unique_id on one rank, its 128 bytes carried to the others by any
  *   means the host program has, then hpspmm_comm_create on every rank (collective).
- * shard plan (collective, synchronises): from the shard's HOST row_ptr / col_idx it lists the rows
- *   of B the shard references per owner (HPSPMM_EXCHANGE_NEEDED_ROWS, and ..._NCCL, which differs in the
- *   transport only) or takes all of them (HPSPMM_EXCHANGE_ALL_ROWS, the plain all-gather), renumbers the shard's columns into that list,
- *   tells every owner which rows to send, and keeps device copies of row_ptr and the renumbered
- *   columns.  Every rank must pass the same b_bounds, max_K and exchange mode.
+ * shard plan (collective, synchronises): from the shard's HOST row_ptr / col_idx it lists the rows of B
+ *   the shard references per owner (HPSPMM_EXCHANGE_NEEDED_ROWS, and ..._NCCL, which differs in the
+ *   transport only) or takes all of them (HPSPMM_EXCHANGE_ALL_ROWS, the plain all-gather), renumbers
+ *   the shard's columns into that list, tells every owner which rows to send, and keeps device copies
+ *   of row_ptr and the renumbered columns.  Every rank must pass the same b_bounds, max_K and mode.
  * exchange_begin: enqueues, on the plan's own stream and after what `stream` holds now, the transfer
  *   of the rows the other ranks need: one kernel that stores them into the receivers' operands over
- *   NVLink followed by a four-byte NCCL all-reduce as the completion signal, or (the NCCL transports) a
- *   packing kernel and one grouped send / receive.  Remote rows land in this GPU's own memory before any
- *   product reads them.  A slot must not be begun again before its product has been enqueued.  product: waits (stream event) for that slot's rows, then runs the local
- *   product on `stream`.  Slots 0..3 are independent buffers: begin several products, then multiply
- *   them in turn, and each exchange overlaps the previous product.  All ranks must issue their begins
- *   in the same order.  The first use of a slot (or a wider K on it) allocates and synchronises.
+ *   NVLink followed by a four-byte NCCL all-reduce as the completion signal, or (the NCCL transports)
+ *   a packing kernel and one grouped send / receive.  Remote rows land in this GPU's own memory
+ *   before any product reads them.  A slot must not be begun again before its product has been
+ *   enqueued.  If some rank cannot map another rank's buffers (no peer access, IPC not permitted),
+ *   all ranks switch together to the NCCL transport.
+ * product: waits (stream event) for that slot's rows, then runs the local product on `stream`.
+ *   Slots 0..3 are independent buffers: begin several products, then multiply them in turn, and each
+ *   exchange overlaps the previous product.  All ranks must issue their begins in the same order.
+ *   The first use of a slot (or a wider K on it) allocates, is collective, and synchronises.
  * hpspmm_spmm_sharded_f32 = exchange_begin + product on slot 0.
  * destroy: collective when world > 1 and a slot was used (the ranks unmap each other's buffers, meet, then
  *   free their own); call it once the last product has completed on this rank, before hpspmm_comm_destroy.
  * vals: the shard's values (device, nnz_local); B_own: rows_own x K (device); C_local: M_local x K.
- * No kernel reads another GPU's memory and nothing waits on the device: ordering is by stream events. */
+ * No kernel reads another GPU's memory and nothing waits on the device: ordering is by stream events
+ * and by the completion of NCCL operations. */
 typedef struct hpspmm_comm hpspmm_comm;
 typedef struct hpspmm_shard_plan hpspmm_shard_plan;
 enum { HPSPMM_COMM_ID_BYTES = 128 };
