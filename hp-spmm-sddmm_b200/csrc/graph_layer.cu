@@ -78,6 +78,7 @@ extern "C" {
 int hpspmm_layer_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
                         const int32_t* col_idx, const float* vals, int64_t max_K, hpspmm_stream stream,
                         hpspmm_layer** out) {
+  HPSPMM_TRACE("hpspmm_layer_create");
   HPSPMM_REQUIRE(ctx, ctx != nullptr && out != nullptr, "null context or output");
   *out = nullptr;
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0 && max_K >= 1, "bad size");
@@ -149,6 +150,7 @@ int hpspmm_layer_transposed(const hpspmm_layer* g, const int32_t** row_ptr_t, co
 
 int hpspmm_layer_forward(hpspmm_ctx* ctx, hpspmm_layer* g, int64_t K, const float* H, float* C,
                          hpspmm_stream stream) {
+  HPSPMM_TRACE("hpspmm_layer_forward");
   HPSPMM_REQUIRE(ctx, ctx != nullptr && g != nullptr, "null context or layer");
   HPSPMM_REQUIRE(ctx, K >= 1 && K <= g->max_K, "K outside [1, max_K] of the layer");
   int cls;
@@ -160,6 +162,7 @@ int hpspmm_layer_forward(hpspmm_ctx* ctx, hpspmm_layer* g, int64_t K, const floa
 
 int hpspmm_layer_backward_features(hpspmm_ctx* ctx, hpspmm_layer* g, int64_t K, const float* dC,
                                    float* dH, hpspmm_stream stream) {
+  HPSPMM_TRACE("hpspmm_layer_backward_features");
   HPSPMM_REQUIRE(ctx, ctx != nullptr && g != nullptr, "null context or layer");
   HPSPMM_REQUIRE(ctx, K >= 1 && K <= g->max_K, "K outside [1, max_K] of the layer");
   int cls;
@@ -171,6 +174,7 @@ int hpspmm_layer_backward_features(hpspmm_ctx* ctx, hpspmm_layer* g, int64_t K, 
 
 int hpspmm_layer_backward_weights(hpspmm_ctx* ctx, hpspmm_layer* g, int64_t K, const float* dC,
                                   const float* H, float* dA, hpspmm_stream stream) {
+  HPSPMM_TRACE("hpspmm_layer_backward_weights");
   HPSPMM_REQUIRE(ctx, ctx != nullptr && g != nullptr, "null context or layer");
   HPSPMM_REQUIRE(ctx, K >= 1 && K <= g->max_K, "K outside [1, max_K] of the layer");
   int cls;

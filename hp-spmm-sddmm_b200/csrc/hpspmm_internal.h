@@ -101,6 +101,18 @@ static inline cudaError_t hpspmm_device_malloc(T** out, size_t bytes) {
   return hpspmm_device_malloc(reinterpret_cast<void**>(out), bytes);
 }
 
+// A named range around an entry point for timeline tools (NVTX 3, header-only: nothing to link, and a call is a
+// null-pointer test when no tool is attached).  The reference has no tracing beyond its event timer
+// (include/spmm/utils/timer_cuda.h:6-40).
+#include <nvtx3/nvToolsExt.h>
+struct hpspmm_trace_range {
+  explicit hpspmm_trace_range(const char* name) { nvtxRangePushA(name); }
+  ~hpspmm_trace_range() { nvtxRangePop(); }
+  hpspmm_trace_range(const hpspmm_trace_range&) = delete;
+  hpspmm_trace_range& operator=(const hpspmm_trace_range&) = delete;
+};
+#define HPSPMM_TRACE(name) hpspmm_trace_range hpspmm_trace_range__(name)
+
 int hpspmm_ensure_scratch(hpspmm_ctx* ctx, size_t bytes);
 int hpspmm_ensure_stage(hpspmm_ctx* ctx, size_t bytes);
 

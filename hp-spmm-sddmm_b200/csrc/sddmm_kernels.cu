@@ -269,6 +269,7 @@ extern "C" int hpspmm_sddmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, in
                                     const int32_t* col_idx, const float* X, const float* Y,
                                     float* out_vals, const hpspmm_opts* opts,
                                     hpspmm_stream stream) {
+  HPSPMM_TRACE("hpspmm_sddmm_csr_f32");
   HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "negative size");
   HPSPMM_REQUIRE(ctx, K >= 1, "K must be >= 1");

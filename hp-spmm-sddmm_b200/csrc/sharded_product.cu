@@ -443,6 +443,7 @@ int hpspmm_comm_info(const hpspmm_comm* comm, int32_t* world, int32_t* rank) {
 int hpspmm_shard_plan_create(hpspmm_ctx* ctx, hpspmm_comm* comm, int64_t M_local, int64_t N, int64_t nnz_local,
                              const int32_t* row_ptr_host, const int32_t* col_idx_host, const int64_t* b_bounds,
                              int64_t max_K, int32_t exchange, hpspmm_stream stream, hpspmm_shard_plan** out) {
+  HPSPMM_TRACE("hpspmm_shard_plan_create");
   HPSPMM_REQUIRE(ctx, ctx != nullptr && out != nullptr, "null context or output");
   *out = nullptr;
   HPSPMM_REQUIRE(ctx, comm != nullptr && comm->device == ctx->device, "communicator missing or on another device");
@@ -669,6 +670,7 @@ int hpspmm_shard_plan_info(const hpspmm_shard_plan* p, int64_t* rows_local, int6
 
 int hpspmm_sharded_exchange_begin(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int32_t slot, int64_t K, const float* B_own,
                                   hpspmm_stream stream) {
+  HPSPMM_TRACE("hpspmm_sharded_exchange_begin");
   HPSPMM_REQUIRE(ctx, ctx != nullptr && p != nullptr, "null context or plan");
   HPSPMM_REQUIRE(ctx, p->device == ctx->device, "plan built on another device");
   HPSPMM_REQUIRE(ctx, slot >= 0 && slot < kSlots, "slot out of range");
@@ -768,6 +770,7 @@ int hpspmm_sharded_exchange_begin(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int32_t
 
 int hpspmm_sharded_product(hpspmm_ctx* ctx, hpspmm_shard_plan* p, int32_t slot, int64_t K, const float* vals,
                            float* C_local, const hpspmm_opts* opts, hpspmm_stream stream) {
+  HPSPMM_TRACE("hpspmm_sharded_product");
   HPSPMM_REQUIRE(ctx, ctx != nullptr && p != nullptr, "null context or plan");
   HPSPMM_REQUIRE(ctx, slot >= 0 && slot < kSlots, "slot out of range");
   hpspmm_shard_slot& s = p->slots[slot];

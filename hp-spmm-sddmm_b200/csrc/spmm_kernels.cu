@@ -1321,6 +1321,7 @@ extern "C" {
 int hpspmm_plan_create(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
                        const int32_t* col_idx, int64_t max_K, const hpspmm_opts* opts,
                        hpspmm_stream stream, hpspmm_plan** out) {
+  HPSPMM_TRACE("hpspmm_plan_create");
   HPSPMM_REQUIRE(ctx, ctx != nullptr && out != nullptr, "null context or output");
   *out = nullptr;
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0 && max_K >= 1, "bad size");
@@ -1452,6 +1453,7 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
                         int64_t nnz, const int32_t* row_ptr, const int32_t* col_idx,
                         const float* vals, const float* B, float* C, const hpspmm_opts* opts,
                         hpspmm_stream stream) {
+  HPSPMM_TRACE("hpspmm_spmm_csr_f32");
   int st = check_spmm_args(ctx, M, N, K, nnz, row_ptr, col_idx, vals, B, C);
   if (st != HPSPMM_OK) return st;
   if (M == 0) return HPSPMM_OK;
@@ -1651,6 +1653,7 @@ static int host_product_slabs(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, 
 int hpspmm_spmm_csr_f32_host_multi(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
                                    const int32_t* col_idx, const float* vals, int32_t n_products, const int64_t* Ks,
                                    const float* const* Bs, float* const* Cs, const hpspmm_opts* opts) {
+  HPSPMM_TRACE("hpspmm_spmm_csr_f32_host_multi");
   HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "bad size");
   HPSPMM_REQUIRE(ctx, n_products >= 0 && n_products <= 16, "between 0 and 16 products per call");
@@ -1692,6 +1695,7 @@ int hpspmm_spmm_csr_f32_host_multi(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_
 int hpspmm_spmm_csr_f32_host(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz,
                              const int32_t* row_ptr, const int32_t* col_idx, const float* vals,
                              const float* B, float* C, const hpspmm_opts* opts) {
+  HPSPMM_TRACE("hpspmm_spmm_csr_f32_host");
   HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0 && K >= 1, "bad size");
   HPSPMM_REQUIRE(ctx, row_ptr != nullptr, "null row_ptr");
@@ -1732,6 +1736,7 @@ int hpspmm_spmm_csr_f32_host(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, i
 int hpspmm_spmm_coo_f32(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nnz_padded,
                         const int32_t* row_idx, const int32_t* col_idx, const float* vals,
                         const float* B, float* C, const hpspmm_opts* opts, hpspmm_stream stream) {
+  HPSPMM_TRACE("hpspmm_spmm_coo_f32");
   HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz_padded >= 0 && K >= 1, "bad size");
   if (nnz_padded == 0 || M == 0) return HPSPMM_OK;

@@ -555,6 +555,7 @@ int hpspmm_csr_to_coo_padded(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int3
 int hpspmm_csr_transpose(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, const int32_t* row_ptr,
                          const int32_t* col_idx, const float* vals, int32_t* row_ptr_t,
                          int32_t* col_idx_t, float* vals_t, int32_t* perm_out, hpspmm_stream stream) {
+  HPSPMM_TRACE("hpspmm_csr_transpose");
   HPSPMM_REQUIRE(ctx, ctx != nullptr, "null context");
   HPSPMM_REQUIRE(ctx, M >= 0 && N >= 0 && nnz >= 0, "negative size");
   if (M > 2147483646ll || N > 2147483646ll || nnz > 2147483647ll) return HPSPMM_ERR_UNSUPPORTED;
