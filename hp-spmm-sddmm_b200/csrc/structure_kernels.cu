@@ -24,6 +24,24 @@ __device__ __forceinline__ int row_of_entry(const int* __restrict__ row_ptr, int
   return r < 0 ? 0 : (r > M - 1 ? M - 1 : r);
 }
 
+// The same search by a whole block (every thread must call it, every thread gets the answer): each round
+// probes blockDim.x evenly spaced candidates at once, so a million rows take three rounds of one load
+// each instead of twenty dependent loads.
+__device__ __forceinline__ int row_of_entry_by_block(const int* __restrict__ row_ptr, int M, int j) {
+  int64_t lo = 0, hi = (int64_t)M + 1;           // row_ptr[lo] <= j always holds (row_ptr[0] = 0)
+  while (hi - lo > 1) {
+    const int64_t step = (hi - lo + blockDim.x - 1) / blockDim.x;
+    const int64_t r = lo + (int64_t)threadIdx.x * step;
+    const int below = __syncthreads_count(r < hi && __ldg(row_ptr + r) <= j);   // >= 1: thread 0 probes lo
+    const int64_t new_lo = lo + (int64_t)(below - 1) * step;
+    const int64_t new_hi = new_lo + step;
+    lo = new_lo;
+    hi = new_hi < hi ? new_hi : hi;
+  }
+  const int r = (int)lo;
+  return r > M - 1 ? M - 1 : r;
+}
+
 // ---- validation ------------------------------------------------------------------------
 // bad[0] = smallest offending position + 1 (rows first, then M + 1 + entry index), 0 if none
 __global__ void validate_csr_kernel(int64_t M, int64_t N, int64_t nnz, const int* __restrict__ row_ptr,
@@ -46,20 +64,76 @@ __global__ void validate_csr_kernel(int64_t M, int64_t N, int64_t nnz, const int
 }
 
 // ---- CSR -> COO ------------------------------------------------------------------------
-__global__ void expand_rows_kernel(int M, int64_t nnz, int64_t padded, const int* __restrict__ row_ptr,
-                                   const int* __restrict__ col_idx, const float* __restrict__ vals,
-                                   int* __restrict__ row_out, int* __restrict__ col_out,
-                                   float* __restrict__ val_out) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < padded; j += stride) {
-    if (j < nnz) {
-      row_out[j] = row_of_entry(row_ptr, M, (int)j);
-      if (col_out) col_out[j] = col_idx[j];
-      if (val_out) val_out[j] = vals[j];
-    } else {
-      row_out[j] = 0;
-      if (col_out) col_out[j] = 0;
-      if (val_out) val_out[j] = 0.f;
+// One block per tile of 4096 entries.  The rows that begin inside the tile mark their first entry with
+// their index (empty rows share a position with the row that owns it; the largest index wins, which is
+// the owner); a running maximum over the tile then gives every entry its row.  Two binary searches per
+// tile instead of one per entry, and every global access is coalesced.  Positions past nnz are padding
+// and receive zeros.  PAIRS writes (row, value bits) as one 8-byte word per entry instead of the arrays.
+constexpr int kExpandTile = 4096;
+template <bool PAIRS>
+__global__ void __launch_bounds__(kThreads)
+expand_rows_kernel(int M, int64_t nnz, int64_t padded, const int* __restrict__ row_ptr,
+                   const int* __restrict__ col_idx, const float* __restrict__ vals, int* __restrict__ row_out,
+                   int* __restrict__ col_out, float* __restrict__ val_out, int2* __restrict__ pair_out) {
+  constexpr int kWarpsHere = kThreads / 32;
+  constexpr int kSpan = kExpandTile / kWarpsHere;     // contiguous entries per warp
+  __shared__ int head[kExpandTile];
+  __shared__ int warp_max[kWarpsHere];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t start = (int64_t)blockIdx.x * kExpandTile;
+  const int live = (int)(nnz - start < kExpandTile ? (nnz > start ? nnz - start : 0) : kExpandTile);
+  if (live > 0) {
+    for (int i = threadIdx.x; i < kExpandTile; i += kThreads) head[i] = -1;
+    const int r_first = row_of_entry_by_block(row_ptr, M, (int)start);
+    const int r_last = row_of_entry_by_block(row_ptr, M, (int)(start + live - 1));
+    for (int r = r_first + threadIdx.x; r <= r_last; r += kThreads) {
+      const int64_t p = (int64_t)__ldg(row_ptr + r) - start;
+      if (p < live) atomicMax(&head[p < 0 ? 0 : (int)p], r);
+    }
+    __syncthreads();
+    int m = -1;
+#pragma unroll 4
+    for (int s = 0; s < kSpan / 32; ++s) m = max(m, head[warp * kSpan + s * 32 + lane]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) warp_max[warp] = m;
+    __syncthreads();
+  }
+  int carry = -1;
+  if (live > 0)
+    for (int w = 0; w < warp; ++w) carry = max(carry, warp_max[w]);
+  // what the tile copies is fetched before the scan, all loads in flight at once
+  constexpr int kStepsHere = kSpan / 32;
+  int c_in[PAIRS ? 1 : kStepsHere];
+  float v_in[kStepsHere];
+#pragma unroll
+  for (int s = 0; s < kStepsHere; ++s) {
+    const int i = warp * kSpan + s * 32 + lane;
+    const int64_t j = start + i;
+    v_in[s] = i < live && vals && (PAIRS || val_out) ? vals[j] : 0.f;
+    if (!PAIRS) c_in[s] = i < live && col_out ? col_idx[j] : 0;
+  }
+#pragma unroll
+  for (int s = 0; s < kStepsHere; ++s) {
+    const int i = warp * kSpan + s * 32 + lane;
+    const int64_t j = start + i;
+    int r = i < live ? head[i] : -1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, r, o);
+      if (lane >= o) r = max(r, t);
+    }
+    r = max(r, carry);
+    carry = __shfl_sync(0xffffffffu, r, 31);
+    if (j < padded) {
+      const int row = i < live ? r : 0;
+      if (PAIRS) {
+        pair_out[j] = make_int2(row, __float_as_int(v_in[s]));
+      } else {
+        row_out[j] = row;
+        if (col_out) col_out[j] = c_in[s];
+        if (val_out) val_out[j] = v_in[s];
+      }
     }
   }
 }
@@ -138,10 +212,21 @@ scan_rescan_kernel(int* __restrict__ data, int64_t n, const int* __restrict__ to
   const int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * per;
   int v[per];
   int s = 0;
+  // a thread's 16 values are 64 contiguous bytes: four 16-byte accesses when the tile is full and aligned
+  const bool vec = per % 4 == 0 && base + per <= n && (reinterpret_cast<uintptr_t>(data) & 15) == 0;
+  if (vec) {
 #pragma unroll
-  for (int i = 0; i < per; ++i) {
-    v[i] = base + i < n ? data[base + i] : 0;
-    s += v[i];
+    for (int i = 0; i < per; i += 4) {
+      const int4 q = *reinterpret_cast<const int4*>(data + base + i);
+      v[i] = q.x, v[i + 1] = q.y, v[i + 2] = q.z, v[i + 3] = q.w;
+      s += q.x + q.y + q.z + q.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < per; ++i) {
+      v[i] = base + i < n ? data[base + i] : 0;
+      s += v[i];
+    }
   }
   part[threadIdx.x] = s;
   __syncthreads();
@@ -152,10 +237,22 @@ scan_rescan_kernel(int* __restrict__ data, int64_t n, const int* __restrict__ to
     __syncthreads();
   }
   int run = totals_scanned[blockIdx.x] + part[threadIdx.x] - s;
+  if (vec) {
 #pragma unroll
-  for (int i = 0; i < per; ++i) {
-    if (base + i < n) data[base + i] = run;
-    run += v[i];
+    for (int i = 0; i < per; i += 4) {
+      int4 q;
+      q.x = run, run += v[i];
+      q.y = run, run += v[i + 1];
+      q.z = run, run += v[i + 2];
+      q.w = run, run += v[i + 3];
+      *reinterpret_cast<int4*>(data + base + i) = q;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < per; ++i) {
+      if (base + i < n) data[base + i] = run;
+      run += v[i];
+    }
   }
 }
 
@@ -219,15 +316,106 @@ radix_scatter_kernel(const int* __restrict__ keys_in, const int* __restrict__ pa
   }
 }
 
-// row_ptr_t[c] = number of sorted keys < c
-__global__ void transposed_row_ptr_kernel(const int* __restrict__ sorted_keys, int64_t nnz, int64_t N,
-                                          int* __restrict__ row_ptr_t) {
+// ---- transpose passes: (column, entry position) pairs, digits of 8, 10 or 11 bits -------------
+// The transpose sorts 64-bit (key, payload) pairs so that a pass moves one 8-byte word per entry, and
+// takes digits wide enough for two passes up to 2^22 columns.  Per-warp digit counts are 16-bit (a warp
+// owns kWarpSpan = 512 keys), which keeps 2048 bins x 8 warps inside the static shared-memory limit.
+template <int DBITS>
+__global__ void __launch_bounds__(kThreads)
+pair_hist_kernel(const int* __restrict__ keys, const int2* __restrict__ pairs, int64_t n, int shift,
+                 int n_tiles, int* __restrict__ hist) {
+  constexpr int D = 1 << DBITS;
+  __shared__ int cnt[D];
+  for (int d = threadIdx.x; d < D; d += kThreads) cnt[d] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * kTile;
+  int k[kItems];
+#pragma unroll
+  for (int i = 0; i < kItems; ++i) {
+    const int64_t idx = base + (int64_t)i * kThreads + threadIdx.x;
+    k[i] = idx < n ? (pairs ? pairs[idx].x : keys[idx]) : -1;
+  }
+#pragma unroll
+  for (int i = 0; i < kItems; ++i)
+    if (k[i] >= 0) atomicAdd(&cnt[(k[i] >> shift) & (D - 1)], 1);
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += kThreads) hist[(int64_t)d * n_tiles + blockIdx.x] = cnt[d];
+}
+
+// Stable scatter of one digit, same ranking scheme as radix_scatter_kernel.  pairs_in == nullptr is the
+// first pass: key i is keys_in[i] and its payload is i.
+template <int DBITS>
+__global__ void __launch_bounds__(kThreads, 3)
+pair_scatter_kernel(const int* __restrict__ keys_in, const int2* __restrict__ pairs_in, int64_t n, int shift,
+                    int n_tiles, const int* __restrict__ hist_scanned, int2* __restrict__ pairs_out) {
+  constexpr int D = 1 << DBITS;
+  __shared__ unsigned short cnt[kWarps][D];
+  __shared__ int tile_base[D];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < kWarps * D; i += kThreads) (&cnt[0][0])[i] = 0;
+  __syncthreads();
+
+  const int64_t wbase = (int64_t)blockIdx.x * kTile + (int64_t)warp * kWarpSpan;
+  // The keys are fetched up front, all loads in flight at once: the ranking loop below synchronises the
+  // warp at every step, and a load issued inside it would wait out its whole latency sixteen times.
+  // Payloads are not held; the scatter reads them again (the tile is 32 KB and still in cache).
+  int key[kSteps];
+  unsigned short rank[kSteps];
+#pragma unroll
+  for (int s = 0; s < kSteps; ++s) {
+    const int64_t idx = wbase + s * 32 + lane;
+    key[s] = idx < n ? (pairs_in ? pairs_in[idx].x : keys_in[idx]) : 0;
+  }
+#pragma unroll
+  for (int s = 0; s < kSteps; ++s) {
+    const int64_t idx = wbase + s * 32 + lane;
+    const bool valid = idx < n;
+    const int k = key[s];
+    const int d = (k >> shift) & (D - 1);
+    const unsigned peers = __match_any_sync(0xffffffffu, valid ? d : (0x10000 | lane));
+    const int leader = __ffs(peers) - 1;
+    int before = 0;
+    if (valid && lane == leader) {
+      before = cnt[warp][d];
+      cnt[warp][d] = (unsigned short)(before + __popc(peers));
+    }
+    before = __shfl_sync(0xffffffffu, before, leader);
+    rank[s] = (unsigned short)(before + __popc(peers & ((1u << lane) - 1u)));
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += kThreads) {
+    // per-warp counts -> offsets of each warp's keys inside the tile's run of digit d
+    int run = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const int t = cnt[w][d];
+      cnt[w][d] = (unsigned short)run;
+      run += t;
+    }
+    tile_base[d] = hist_scanned[(int64_t)d * n_tiles + blockIdx.x];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int s = 0; s < kSteps; ++s) {
+    const int64_t idx = wbase + s * 32 + lane;
+    if (idx < n) {
+      const int d = (key[s] >> shift) & (D - 1);
+      pairs_out[tile_base[d] + cnt[warp][d] + rank[s]] = make_int2(key[s], pairs_in ? pairs_in[idx].y : (int)idx);
+    }
+  }
+}
+
+// row_ptr_t[c] = number of sorted pairs with key < c
+__global__ void transposed_row_ptr_pairs_kernel(const int2* __restrict__ sorted, int64_t nnz, int64_t N,
+                                                int* __restrict__ row_ptr_t) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c <= N; c += stride) {
     int64_t lo = 0, hi = nnz;
     while (lo < hi) {
       const int64_t mid = (lo + hi) >> 1;
-      if ((int64_t)sorted_keys[mid] < c)
+      if ((int64_t)__ldg(&sorted[mid].x) < c)
         lo = mid + 1;
       else
         hi = mid;
@@ -236,19 +424,31 @@ __global__ void transposed_row_ptr_kernel(const int* __restrict__ sorted_keys, i
   }
 }
 
-// col_idx_t[t] = source row of transposed entry t, looked up in the expanded row-index array
-// (one random 4-byte read instead of a binary search over row_ptr per entry)
-__global__ void transposed_gather_kernel(int64_t nnz, const int* __restrict__ row_of,
-                                         const float* __restrict__ vals, const int* __restrict__ perm,
-                                         int* __restrict__ col_idx_t, float* __restrict__ vals_t,
-                                         int* __restrict__ perm_out) {
+// transposed entry t comes from entry sorted[t].y of the source: its row becomes the column index
+__global__ void transposed_emit_kernel(int64_t nnz, const int2* __restrict__ sorted,
+                                       const int2* __restrict__ row_val, int* __restrict__ col_idx_t,
+                                       float* __restrict__ vals_t, int* __restrict__ perm_out) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nnz; t += stride) {
-    const int j = perm[t];
-    col_idx_t[t] = __ldg(row_of + j);
-    if (vals_t) vals_t[t] = __ldg(vals + j);
+    const int j = sorted[t].y;
+    const int2 e = __ldg(row_val + j);
+    col_idx_t[t] = e.x;
+    if (vals_t) vals_t[t] = __int_as_float(e.y);
     if (perm_out) perm_out[t] = j;
   }
+}
+
+// one pass: histogram per tile and digit, exclusive scan of the digit-major matrix, stable scatter
+template <int DBITS>
+void launch_pair_pass(const int* keys_in, const int2* pairs_in, int64_t n, int shift, int n_tiles, int* hist,
+                      int* totals, int2* pairs_out, cudaStream_t s) {
+  const int64_t hist_n = ((int64_t)1 << DBITS) * n_tiles;
+  const int64_t scan_blocks = (hist_n + kScanTile - 1) / kScanTile;
+  pair_hist_kernel<DBITS><<<n_tiles, kThreads, 0, s>>>(keys_in, pairs_in, n, shift, n_tiles, hist);
+  scan_block_totals_kernel<<<(unsigned)scan_blocks, kThreads, 0, s>>>(hist, hist_n, totals);
+  scan_single_block_kernel<<<1, kThreads, 0, s>>>(totals, scan_blocks);
+  scan_rescan_kernel<<<(unsigned)scan_blocks, kThreads, 0, s>>>(hist, hist_n, totals);
+  pair_scatter_kernel<DBITS><<<n_tiles, kThreads, 0, s>>>(keys_in, pairs_in, n, shift, n_tiles, hist, pairs_out);
 }
 
 // Sort key of chunk c (ascending = earlier).  Without col_idx: 255 - cost (8 bits).  With col_idx, 16 bits:
@@ -545,8 +745,8 @@ int hpspmm_csr_to_coo_padded(hpspmm_ctx* ctx, int64_t M, int64_t nnz, const int3
   HPSPMM_REQUIRE(ctx, row_ptr && row_out, "null pointer");
   HPSPMM_REQUIRE(ctx, (!col_out || col_idx) && (!val_out || vals), "missing source array");
   hpspmm_device_guard guard(ctx->device);
-  expand_rows_kernel<<<grid_for(ctx, padded), kThreads, 0, (cudaStream_t)stream>>>(
-      (int)M, nnz, padded, row_ptr, col_idx, vals, row_out, col_out, val_out);
+  expand_rows_kernel<false><<<(unsigned)((padded + kExpandTile - 1) / kExpandTile), kThreads, 0, (cudaStream_t)stream>>>(
+      (int)M, nnz, padded, row_ptr, col_idx, vals, row_out, col_out, val_out, nullptr);
   ctx->launches++;
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;
@@ -568,49 +768,48 @@ int hpspmm_csr_transpose(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_t nnz, con
     HPSPMM_CUDA_TRY(ctx, cudaMemsetAsync(row_ptr_t, 0, (size_t)(N + 1) * 4, s));
     return HPSPMM_OK;
   }
+  // digits: as few passes as 11-bit digits allow, each as narrow as that number of passes permits
   int bits = 1;
   while (bits < 31 && ((int64_t)1 << bits) < N) ++bits;
-  const int passes = (bits + 7) / 8;
+  const int passes = (bits + 10) / 11;
+  const int need = (bits + passes - 1) / passes;
+  const int dbits = need <= 8 ? 8 : (need <= 10 ? 10 : 11);
   const int n_tiles = (int)((nnz + kTile - 1) / kTile);
-  const int64_t hist_n = (int64_t)256 * n_tiles;
+  const int64_t hist_n = ((int64_t)1 << dbits) * n_tiles;
   const int64_t scan_blocks = (hist_n + kScanTile - 1) / kScanTile;
-  const size_t b_arr = align_up((size_t)nnz * 4, 256);
+  const size_t b_pairs = align_up((size_t)nnz * 8, 256);
   const size_t b_hist = align_up((size_t)hist_n * 4, 256);
   const size_t b_tot = align_up((size_t)scan_blocks * 4, 256);
-  int st = hpspmm_ensure_scratch(ctx, 5 * b_arr + b_hist + b_tot);
+  int st = hpspmm_ensure_scratch(ctx, 3 * b_pairs + b_hist + b_tot);
   if (st != HPSPMM_OK) return st;
   char* base = (char*)ctx->scratch;
-  int* keys[2] = {(int*)base, (int*)(base + b_arr)};
-  int* pays[2] = {(int*)(base + 2 * b_arr), (int*)(base + 3 * b_arr)};
-  int* row_of = (int*)(base + 4 * b_arr);
-  int* hist = (int*)(base + 5 * b_arr);
-  int* totals = (int*)(base + 5 * b_arr + b_hist);
+  int2* pairs[2] = {(int2*)base, (int2*)(base + b_pairs)};
+  int2* row_val = (int2*)(base + 2 * b_pairs);
+  int* hist = (int*)(base + 3 * b_pairs);
+  int* totals = (int*)(base + 3 * b_pairs + b_hist);
 
-  // source row of every entry (neighbouring threads search neighbouring entries: cache friendly)
-  expand_rows_kernel<<<grid_for(ctx, nnz), kThreads, 0, s>>>((int)M, nnz, nnz, row_ptr, nullptr, nullptr,
-                                                             row_of, nullptr, nullptr);
+  // (source row, value) of every entry as one word, so that the final gather reads one sector per entry
+  expand_rows_kernel<true><<<(unsigned)((nnz + kExpandTile - 1) / kExpandTile), kThreads, 0, s>>>(
+      (int)M, nnz, nnz, row_ptr, nullptr, vals, nullptr, nullptr, nullptr, row_val);
   ctx->launches++;
 
-  const int* kin = col_idx;
-  const int* pin = nullptr;
+  const int2* pin = nullptr;
   int cur = 0;
   for (int p = 0; p < passes; ++p) {
-    const int shift = 8 * p;
-    radix_hist_kernel<<<n_tiles, kThreads, 0, s>>>(kin, nnz, shift, n_tiles, hist);
-    scan_block_totals_kernel<<<(unsigned)scan_blocks, kThreads, 0, s>>>(hist, hist_n, totals);
-    scan_single_block_kernel<<<1, kThreads, 0, s>>>(totals, scan_blocks);
-    scan_rescan_kernel<<<(unsigned)scan_blocks, kThreads, 0, s>>>(hist, hist_n, totals);
-    radix_scatter_kernel<<<n_tiles, kThreads, 0, s>>>(kin, pin, nnz, shift, n_tiles, hist, keys[cur],
-                                                      pays[cur]);
+    const int shift = dbits * p;
+    if (dbits == 8)
+      launch_pair_pass<8>(col_idx, pin, nnz, shift, n_tiles, hist, totals, pairs[cur], s);
+    else if (dbits == 10)
+      launch_pair_pass<10>(col_idx, pin, nnz, shift, n_tiles, hist, totals, pairs[cur], s);
+    else
+      launch_pair_pass<11>(col_idx, pin, nnz, shift, n_tiles, hist, totals, pairs[cur], s);
     ctx->launches += 5;
     HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
-    kin = keys[cur];
-    pin = pays[cur];
+    pin = pairs[cur];
     cur ^= 1;
   }
-  transposed_row_ptr_kernel<<<grid_for(ctx, N + 1), kThreads, 0, s>>>(kin, nnz, N, row_ptr_t);
-  transposed_gather_kernel<<<grid_for(ctx, nnz), kThreads, 0, s>>>(nnz, row_of, vals, pin, col_idx_t,
-                                                                   vals_t, perm_out);
+  transposed_row_ptr_pairs_kernel<<<grid_for(ctx, N + 1), kThreads, 0, s>>>(pin, nnz, N, row_ptr_t);
+  transposed_emit_kernel<<<grid_for(ctx, nnz), kThreads, 0, s>>>(nnz, pin, row_val, col_idx_t, vals_t, perm_out);
   ctx->launches += 2;
   HPSPMM_CUDA_TRY(ctx, cudaGetLastError());
   return HPSPMM_OK;

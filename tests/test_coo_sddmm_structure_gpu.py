@@ -133,15 +133,33 @@ def test_sddmm_edge_structures(gpu_ctx, pkg, oracle):
                 b.free()
 
 
-@pytest.mark.parametrize("shape", ["rmat13", "rect", "tiny", "wide"])
+@pytest.mark.parametrize("shape", ["rmat13", "rect", "tiny", "wide", "cols_2_20", "cols_3m", "cols_5m"])
 def test_transpose_bit_exact(gpu_ctx, pkg, oracle, shape):
     ctx = gpu_ctx
     if shape == "rmat13":
-        g = pkg.gen_rmat(13, 16, seed=8)
+        g = pkg.gen_rmat(13, 16, seed=8)     # 13 bits of column index: two passes of 8-bit digits
         M, N, row_ptr, col_idx, vals = g["M"], g["N"], g["row_ptr"], g["col_idx"], g["vals"]
     elif shape == "rect":
-        M, N = 777, 70001     # more than 16 bits of column index: three radix passes
+        M, N = 777, 70001     # 17 bits of column index: two passes of 10-bit digits
         row_ptr, col_idx, vals = random_csr(M, N, np.random.default_rng(1).integers(0, 200, M), seed=1)
+    elif shape.startswith("cols_"):
+        # 20 bits: two 10-bit passes; 22 bits: two 11-bit passes; 23 bits: three 8-bit passes.  Many tiles
+        # of 4096 entries, one heavy row and a hot column block so that digits repeat inside a warp.
+        N = {"cols_2_20": 1 << 20, "cols_3m": 3_000_000, "cols_5m": 5_000_000}[shape]
+        M = 3000
+        rng = np.random.default_rng(N)
+        deg = rng.integers(0, 120, M)
+        deg[17] = 30000
+        row_ptr, col_idx, vals = random_csr(M, N, deg, seed=N % 1000)
+        hot = rng.random(len(col_idx)) < 0.2          # a fifth of the entries fall into 64 columns
+        col_idx = np.where(hot, col_idx % 64, col_idx).astype(np.int32)
+        for r in range(M):                            # keep rows sorted and duplicate-free
+            seg = np.unique(col_idx[row_ptr[r]:row_ptr[r + 1]])
+            col_idx[row_ptr[r]:row_ptr[r] + len(seg)] = seg
+            deg[r] = len(seg)
+        keep = np.concatenate([np.arange(row_ptr[r], row_ptr[r] + deg[r]) for r in range(M)])
+        col_idx, vals = col_idx[keep].copy(), vals[keep].copy()
+        row_ptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
     elif shape == "tiny":
         M, N = 3, 2
         row_ptr, col_idx, vals = random_csr(M, N, [2, 0, 1], seed=2)
