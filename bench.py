@@ -839,8 +839,16 @@ def run_ceilings(pkg):
             gbs, ms = ctx.probe_gather(rb, rows, n, pattern, hot_rows, hot_share, 10)
             out.append({"row_bytes": rb, "pattern": name, "table_mb": rows * rb / 1e6, "ms": ms, "gbs": gbs,
                         "bytes_per_clk_per_sm_at_1.9ghz": gbs * 1e9 / (148 * 1.9e9)})
+    tma = []
+    for rb in (128, 256, 512):
+        for name, rows in (("random rows, 64 MB table (L2-resident)", (64 << 20) // rb),
+                           ("random rows, 546186-row table", 546186)):
+            for ctas in (1, 2, 3):
+                gbs, ms, _, done = ctx.probe_tma_gather(rb, rows, n, ctas, 10)
+                tma.append({"row_bytes": rb, "pattern": name, "ctas_per_sm": ctas, "table_mb": rows * rb / 1e6, "ms": ms,
+                            "gbs": gbs, "gathers": done, "bytes_per_clk_per_sm_at_1.9ghz": gbs * 1e9 / (148 * 1.9e9)})
     ctx.close()
-    print(json.dumps({"ceilings": out, "gathers_per_launch": n}))
+    print(json.dumps({"ceilings": out, "tma_gather4": tma, "gathers_per_launch": n}))
 
 
 def main():

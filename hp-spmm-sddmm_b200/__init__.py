@@ -154,6 +154,8 @@ PROTOTYPES = {
     "hpspmm_debug_fail_device_alloc": (c_int, [_I64, _I64]),
     "hpspmm_probe_gather_gbs": (c_int, [_P, c_int32, _I64, _I64, c_int32, _I64, c_double, c_int32,
                                         POINTER(c_double), POINTER(c_double)]),
+    "hpspmm_probe_tma_gather_gbs": (c_int, [_P, c_int32, _I64, _I64, c_int32, c_int32, POINTER(c_double),
+                                            POINTER(c_double), POINTER(c_double), POINTER(_I64)]),
 }
 
 _lib = None
@@ -421,6 +423,16 @@ class Context:
                                                      hot_rows, hot_share, repeats, byref(gbs), byref(ms)),
                     "hpspmm_probe_gather_gbs")
         return gbs.value, ms.value
+
+    def probe_tma_gather(self, row_bytes, table_rows, n_gathers, ctas_per_sm=2, repeats=10):
+        """The same random rows fetched by TMA gather4 into shared memory (hpspmm_probe_tma_gather_gbs):
+        GB/s, ms per launch, the sum of everything read and the number of gathers per launch."""
+        gbs, ms, checksum, done = c_double(), c_double(), c_double(), _I64()
+        self._check(self.lib.hpspmm_probe_tma_gather_gbs(self.handle, row_bytes, table_rows, n_gathers, ctas_per_sm,
+                                                         repeats, byref(gbs), byref(ms), byref(checksum),
+                                                         byref(done)),
+                    "hpspmm_probe_tma_gather_gbs")
+        return gbs.value, ms.value, checksum.value, done.value
 
 
 # ---- host side ---------------------------------------------------------------------------

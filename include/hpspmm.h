@@ -510,6 +510,22 @@ HPSPMM_API int hpspmm_probe_gather_gbs(hpspmm_ctx* ctx, int32_t row_bytes, int64
                                        double hot_share, int32_t repeats, double* gbs_out,
                                        double* ms_out);
 
+/* The same random rows through the tensor memory accelerator: producer warps fetch four rows per
+ * instruction into shared memory (cp.async.bulk.tensor ... tile::gather4 on a tensor map of the table),
+ * consumer warps read every delivered byte into registers.  row_bytes is 128, 256 or 512; the table is
+ * allocated and filled by the probe (row r holds the value r mod 251 in every column); ctas_per_sm is 1
+ * to 3 (each CTA: four producer and eight consumer warps over four 16 KB buffers).  n_gathers is rounded
+ * up to whole buffers per CTA; *gathers_done_out receives the number performed and *checksum_out the sum
+ * of everything the consumers read, which a caller can replay on the host (gather i reads row
+ * umulhi(((h ^ (h >> 15)) * 2246822519), table_rows) with h = i * 2654435761, 32-bit arithmetic).
+ * Every wait inside the kernel is bounded; one that runs out returns HPSPMM_ERR_CUDA with a message.
+ * HPSPMM_ERR_UNSUPPORTED when the driver has no cuTensorMapEncodeTiled.  The reference has no
+ * counterpart. */
+HPSPMM_API int hpspmm_probe_tma_gather_gbs(hpspmm_ctx* ctx, int32_t row_bytes, int64_t table_rows,
+                                           int64_t n_gathers, int32_t ctas_per_sm, int32_t repeats,
+                                           double* gbs_out, double* ms_out, double* checksum_out,
+                                           int64_t* gathers_done_out);
+
 #ifdef __cplusplus
 }
 #endif
