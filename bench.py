@@ -461,6 +461,28 @@ def run_single(args, pkg):
             del A_t
         except Exception as exc:   # a library column must never fail the bench
             compare["error"] = "%s: %s" % (type(exc).__name__, str(exc)[:200])
+        if 128 in ks:
+            # this library's own alternative at K = 128: the rows of B fetched by TMA gather4 (HPSPMM_ALGO_TMA)
+            try:
+                tma_opts = pkg.Opts(algo=pkg.ALGO_TMA)
+                keep = Cs[128].clone()
+                run_tma = lambda: ctx.spmm_csr(M, N, 128, nnz, t_rp.data_ptr(), t_ci.data_ptr(), t_v.data_ptr(),
+                                               Bs[128].data_ptr(), Cs[128].data_ptr(), plan=plans[128],
+                                               opts=tma_opts, stream=sptr)
+                for _ in range(3):
+                    run_tma()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for _ in range(10):
+                    run_tma()
+                b.record(stream)
+                torch.cuda.synchronize()
+                compare["own_tma_kernel_k128"] = {"ms": a.elapsed_time(b) / 10, "default_kernel_ms": per_k_ms[128],
+                                                  "bit_equal_to_default": bool(torch.equal(keep, Cs[128])),
+                                                  "bounded_waits_that_ran_out": ctx.tma_fallbacks()}
+                del keep
+            except Exception as exc:
+                compare["own_tma_kernel_k128"] = {"error": "%s: %s" % (type(exc).__name__, str(exc)[:200])}
         lib, why = load_ref_lib()
         if lib is not None and ks == KS:
             try:

@@ -33,6 +33,7 @@ ERR_BAD_CSR = 6
 ALGO_AUTO = 0
 ALGO_BALANCED = 1
 ALGO_ROW_SPLIT = 2
+ALGO_TMA = 3
 
 EXCHANGE_NEEDED_ROWS = 0
 EXCHANGE_ALL_ROWS = 1
@@ -154,6 +155,7 @@ PROTOTYPES = {
     "hpspmm_debug_fail_device_alloc": (c_int, [_I64, _I64]),
     "hpspmm_probe_gather_gbs": (c_int, [_P, c_int32, _I64, _I64, c_int32, _I64, c_double, c_int32,
                                         POINTER(c_double), POINTER(c_double)]),
+    "hpspmm_ctx_tma_fallbacks": (c_int, [_P, POINTER(_I64)]),
     "hpspmm_probe_tma_gather_gbs": (c_int, [_P, c_int32, _I64, _I64, c_int32, c_int32, POINTER(c_double),
                                             POINTER(c_double), POINTER(c_double), POINTER(_I64)]),
 }
@@ -423,6 +425,12 @@ class Context:
                                                      hot_rows, hot_share, repeats, byref(gbs), byref(ms)),
                     "hpspmm_probe_gather_gbs")
         return gbs.value, ms.value
+
+    def tma_fallbacks(self):
+        """Warps of the HPSPMM_ALGO_TMA kernel that gave up waiting for a TMA copy (expected 0); synchronises."""
+        n = _I64()
+        self._check(self.lib.hpspmm_ctx_tma_fallbacks(self.handle, byref(n)), "hpspmm_ctx_tma_fallbacks")
+        return n.value
 
     def probe_tma_gather(self, row_bytes, table_rows, n_gathers, ctas_per_sm=2, repeats=10):
         """The same random rows fetched by TMA gather4 into shared memory (hpspmm_probe_tma_gather_gbs):

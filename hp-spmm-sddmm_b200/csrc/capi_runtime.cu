@@ -94,6 +94,16 @@ int hpspmm_ctx_destroy(hpspmm_ctx* ctx) {
 }
 
 const char* hpspmm_last_error(const hpspmm_ctx* ctx) { return ctx ? ctx->err : ""; }
+int hpspmm_ctx_tma_fallbacks(hpspmm_ctx* ctx, int64_t* count) {
+  HPSPMM_REQUIRE(ctx, ctx != nullptr && count != nullptr, "null context or output");
+  hpspmm_device_guard guard(ctx->device);
+  int n = 0;
+  HPSPMM_CUDA_TRY(ctx, cudaDeviceSynchronize());
+  HPSPMM_CUDA_TRY(ctx, cudaMemcpy(&n, ctx->flag + HPSPMM_FLAG_TMA_FALLBACKS, sizeof(int), cudaMemcpyDeviceToHost));
+  *count = n;
+  return HPSPMM_OK;
+}
+
 int hpspmm_ctx_device(const hpspmm_ctx* ctx) { return ctx ? ctx->device : -1; }
 int hpspmm_ctx_sm_count(const hpspmm_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 int64_t hpspmm_ctx_l2_bytes(const hpspmm_ctx* ctx) { return ctx ? ctx->l2_bytes : 0; }

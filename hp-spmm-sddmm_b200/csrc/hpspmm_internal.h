@@ -22,12 +22,16 @@ struct hpspmm_ctx {
   // staging for the host-buffer entry point
   void* stage;
   size_t stage_bytes;
-  int* flag;  // one device int used by validation and plan building
+  int* flag;  // 64 device ints: [0] validation and plan building, [HPSPMM_FLAG_TMA_FALLBACKS] see below
   // streams of the host-buffer entry point: uploads, kernels, downloads (created on first use)
   cudaStream_t pipe_streams[3];
   cudaEvent_t pipe_events[8];   // "A has landed" and, per buffer, slab uploaded / multiplied / downloaded
   char err[256];
 };
+
+// ctx->flag[HPSPMM_FLAG_TMA_FALLBACKS] counts the warps of spmm_tma_kernel whose bounded wait for a TMA copy
+// ran out (they finish their chunk with ordinary loads); hpspmm_ctx_tma_fallbacks reads it.
+#define HPSPMM_FLAG_TMA_FALLBACKS 16
 
 // Chunk table of one sparsity structure.
 //   chunk_start[c]  first nnz of chunk c (n_chunks + 1 entries)

@@ -25,6 +25,8 @@
 #include <mutex>
 #include <new>
 
+#include <cuda.h>   // CUtensorMap and the encode prototype; the entry point is looked up at run time
+
 #include "device_utils.cuh"
 #include "hpspmm_internal.h"
 
@@ -544,6 +546,214 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   __syncwarp();   // every lane's part is visible before lane 0 bumps a counter
   if (stores_split_row) settle_split_row<W>(r0, r0_end, S, row_ptr, carry_val, C, run_counter, (int)K);
   if (hands_on) settle_split_row<W>(row, row_end, S, row_ptr, carry_val, C, run_counter, (int)K);
+}
+
+// ---- K = 128 with the rows of B fetched by TMA ----------------------------------------------------
+// Same chunks, same order of additions and same settlement as spmm_warp_kernel<32, ...>; what differs is
+// how a row of B (512 bytes) reaches the warp.  Lane 0 names four rows at a time to the tensor memory
+// accelerator (cp.async.bulk.tensor ... tile::gather4 on a tensor map of B whose box is one row), which
+// writes them into a ring of kTmaRing 2 KB buffers private to the warp and signals an mbarrier per buffer;
+// the warp reads each row back with one 16-byte shared-memory load per lane.  The gathers of up to
+// kTmaRing groups are in flight while the warp multiplies, whatever its register budget, and they occupy
+// neither the load/store unit's global path nor registers while they travel.
+//
+// The chunk's (column, value) pairs are staged whole (a chunk of nominal size S holds at most 2 S - 1
+// entries, and the launcher takes plans up to S = kTmaMaxS).
+// Every wait is bounded by a clock limit; a warp whose wait runs out counts that in *fallbacks, fetches
+// the rest of its chunk with ordinary loads and, before it leaves, waits (bounded again) for the copies
+// it still has in flight, so a fault in the protocol costs time and leaves a record but neither hangs
+// nor changes the result.
+#ifndef HPSPMM_TMA_RING
+#define HPSPMM_TMA_RING 2
+#endif
+#ifndef HPSPMM_TMA_WARPS
+#define HPSPMM_TMA_WARPS 8
+#endif
+#ifndef HPSPMM_TMA_BATCH
+#define HPSPMM_TMA_BATCH 1
+#endif
+constexpr int kTmaBatch = HPSPMM_TMA_BATCH;        // groups issued per TMA instruction (one per lane)
+constexpr int kTmaRing = HPSPMM_TMA_RING;          // 2 KB buffers per warp, a multiple of kTmaBatch
+#ifndef HPSPMM_TMA_MAX_S
+#define HPSPMM_TMA_MAX_S 256
+#endif
+constexpr int kTmaMaxS = HPSPMM_TMA_MAX_S;         // largest nominal chunk size taken
+constexpr int kTmaMaxChunk = 2 * kTmaMaxS;         // a chunk holds at most 2 S - 1 entries (chunk_table_kernel)
+constexpr int kTmaWarps = HPSPMM_TMA_WARPS;        // warps (= chunks) per block; three blocks per SM
+constexpr int kTmaGroupBytes = 4 * 128 * 4;        // four rows of 128 floats
+constexpr long long kTmaSpinLimit = 1000000000ll;  // clock cycles, about half a second
+static_assert(kTmaRing % kTmaBatch == 0 && kTmaRing >= 2 * kTmaBatch, "ring = whole batches, at least two");
+constexpr int kTmaSmemPerWarp = kTmaRing * kTmaGroupBytes + kTmaMaxChunk * 8 + kTmaRing * 8;
+
+__device__ __forceinline__ uint32_t smem_addr_of(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  for (unsigned n = 1;; ++n) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((n & 63u) == 0 && clock64() - t0 > kTmaSpinLimit) return false;
+  }
+}
+
+__global__ void __launch_bounds__(kTmaWarps * 32, 3)
+spmm_tma_kernel(const __grid_constant__ CUtensorMap map_b, int M, int n_chunks, int n_chunk_blocks,
+                const int* __restrict__ row_ptr, const int* __restrict__ col_idx,
+                const float* __restrict__ vals, const float* __restrict__ B, float* __restrict__ C,
+                const int* __restrict__ chunk_start, const int* __restrict__ chunk_row,
+                float* __restrict__ carry_val, const int* __restrict__ chunk_order, int S,
+                int* __restrict__ run_counter, const int* __restrict__ nz_id, const int* __restrict__ nz_end,
+                const int* __restrict__ chunk_ri, int* __restrict__ fallbacks) {
+  constexpr int KW = 128;
+  constexpr int64_t K = KW;
+  extern __shared__ __align__(1024) unsigned char tma_smem[];
+  if ((int)blockIdx.x >= n_chunk_blocks) {
+    zero_empty_rows(M, KW, row_ptr, C, blockIdx.x - n_chunk_blocks, gridDim.x - n_chunk_blocks, kTmaWarps * 32, K);
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int slot = blockIdx.x * kTmaWarps + warp;
+  if (slot >= n_chunks) return;
+  const int chunk = chunk_order != nullptr ? __ldg(chunk_order + slot) : slot;
+
+  // this warp's part of shared memory: ring buffers (1 KB aligned), staged entries, barriers
+  unsigned char* ring = tma_smem + (size_t)warp * (kTmaRing * kTmaGroupBytes);
+  int2* ent = reinterpret_cast<int2*>(tma_smem + (size_t)kTmaWarps * (kTmaRing * kTmaGroupBytes)) + warp * kTmaMaxChunk;
+  uint64_t* full = reinterpret_cast<uint64_t*>(tma_smem + (size_t)kTmaWarps * (kTmaRing * kTmaGroupBytes + kTmaMaxChunk * 8)) +
+                   warp * kTmaRing;
+
+  const int n0 = __ldg(chunk_start + chunk);
+  const int n1 = __ldg(chunk_start + chunk + 1);
+  const int len = n1 - n0;                  // < kTmaMaxChunk: the launcher checks the plan's chunk size
+  const int n_groups = (len + 3) >> 2;
+  int ri = __ldg(chunk_ri + chunk);
+  int row = __ldg(nz_id + ri);
+  int row_end = __ldg(nz_end + ri);
+
+  for (int i = lane; i < n_groups * 4; i += 32) {
+    if (i < len) {
+      cp_async_4(&ent[i].x, col_idx + n0 + i);
+      cp_async_4(&ent[i].y, vals + n0 + i);
+    } else {
+      ent[i] = make_int2(0, 0);             // past the chunk: row 0 is fetched and not used
+    }
+  }
+  cp_async_commit();
+  if (lane == 0) {
+#pragma unroll
+    for (int b = 0; b < kTmaRing; ++b)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr_of(&full[b])), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  cp_async_wait<0>();
+  __syncwarp();
+
+  // lane 0: fetch the four rows of group g into buffer g % kTmaRing
+  auto issue = [&](int g) {
+    const int b = g % kTmaRing;
+    const uint32_t bar = smem_addr_of(&full[b]);
+    const int4 c01 = *reinterpret_cast<const int4*>(&ent[4 * g]);
+    const int4 c23 = *reinterpret_cast<const int4*>(&ent[4 * g + 2]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kTmaGroupBytes) : "memory");
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(smem_addr_of(ring + (size_t)b * kTmaGroupBytes)),
+        "l"(&map_b), "r"(0), "r"(c01.x), "r"(c01.z), "r"(c23.x), "r"(c23.z), "r"(bar)
+        : "memory");
+  };
+  // One TMA instruction costs the SM about as much as five gather4 operations, so the lanes 0 .. kTmaBatch-1
+  // issue one group each with a single instruction, every kTmaBatch groups.
+  const int ahead = n_groups < kTmaRing ? n_groups : kTmaRing;
+  for (int g0 = 0; g0 < ahead; g0 += kTmaBatch)
+    if (lane < kTmaBatch && g0 + lane < ahead) issue(g0 + lane);
+  int issued = ahead;                        // groups handed to the TMA so far (warp-uniform)
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto finish_row = [&]() {
+    st_stream(C + (int64_t)row * K + lane * 4, acc);
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    ++ri;
+    row = __ldg(nz_id + ri);
+    row_end = __ldg(nz_end + ri);
+  };
+
+  bool by_tma = true;
+  int pending_from = 0;                      // first group whose copy was never seen to land
+  for (int g = 0; g < n_groups; ++g) {
+    const int b = g % kTmaRing;
+    float4 rows4[4];
+    float v[4];
+    const int4 e01 = *reinterpret_cast<const int4*>(&ent[4 * g]);       // (col, val) x 2, broadcast
+    const int4 e23 = *reinterpret_cast<const int4*>(&ent[4 * g + 2]);
+    v[0] = __int_as_float(e01.y), v[1] = __int_as_float(e01.w);
+    v[2] = __int_as_float(e23.y), v[3] = __int_as_float(e23.w);
+    if (by_tma) {
+      const bool ok = mbar_wait_limited(smem_addr_of(&full[b]), (uint32_t)(g / kTmaRing) & 1u);
+      by_tma = __all_sync(0xffffffffu, ok);
+      if (!by_tma) {
+        pending_from = g;
+        if (lane == 0) atomicAdd(fallbacks, 1);
+      }
+    }
+    if (by_tma) {
+      const float4* src = reinterpret_cast<const float4*>(ring + (size_t)b * kTmaGroupBytes) + lane;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) rows4[i] = src[i * 32];
+      __syncwarp();                          // every lane has read the buffer before it is refilled
+      if ((g + 1) % kTmaBatch == 0 && issued < n_groups) {
+        // the kTmaBatch buffers of groups g - kTmaBatch + 1 .. g are free: refill them with the next groups
+        const int n_new = min(kTmaBatch, n_groups - issued);
+        // (the warp's reads of these buffers are ordered before this point by the __syncwarp above; the
+        // refill is ordered after it by program order, as in any mbarrier-released TMA ring)
+        if (lane < n_new) issue(issued + lane);
+        issued += n_new;
+      }
+    } else {
+      const int cols[4] = {e01.x, e01.z, e23.x, e23.z};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) rows4[i] = ld_gather_plain(B + (int64_t)cols[i] * K + lane * 4);
+    }
+    const int j0 = n0 + 4 * g;
+    if (j0 + 4 <= n1 && row_end >= j0 + 4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) fma4(acc, v[i], rows4[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = j0 + i;
+        if (j < n1) {
+          while (row_end <= j) finish_row();   // warp-uniform
+          fma4(acc, v[i], rows4[i]);
+        }
+      }
+    }
+  }
+  if (!by_tma) {
+    // copies still in flight target this block's shared memory: let them land before the warp leaves
+    for (int g = pending_from; g < issued; ++g)
+      mbar_wait_limited(smem_addr_of(&full[g % kTmaRing]), (uint32_t)(g / kTmaRing) & 1u);
+  }
+
+  const bool hands_on = row_end != n1;   // the chunk ends inside `row`
+  if (!hands_on)
+    st_stream(C + (int64_t)row * K + lane * 4, acc);
+  else
+    *reinterpret_cast<float4*>(carry_val + (int64_t)chunk * K + lane * 4) = acc;
+  const int r0 = __ldg(chunk_row + chunk);
+  const int r0_start = __ldg(row_ptr + r0), r0_end = __ldg(row_ptr + r0 + 1);
+  const bool stores_split_row = r0_start < n0 && r0_end <= n1;   // began in an earlier chunk, ends here
+  if (!hands_on && !stores_split_row) return;
+  __threadfence();
+  __syncwarp();
+  if (stores_split_row) settle_split_row<32>(r0, r0_end, S, row_ptr, carry_val, C, run_counter, KW);
+  if (hands_on) settle_split_row<32>(row, row_end, S, row_ptr, carry_val, C, run_counter, KW);
 }
 
 // ---- generic kernel: any K -------------------------------------------------------------
@@ -1158,6 +1368,64 @@ int launch_generic(hpspmm_ctx* ctx, bool rowsplit, int M, int K, int n_chunks,
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+typedef CUresult (*tensor_map_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                         const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                         CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+tensor_map_encode_fn tensor_map_encoder() {
+  static std::once_flag once;
+  static tensor_map_encode_fn fn = nullptr;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult found;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &found) == cudaSuccess &&
+        found == cudaDriverEntryPointSuccess)
+      fn = (tensor_map_encode_fn)p;
+  });
+  return fn;
+}
+
+// The K = 128 product with B fetched by TMA.  Returns 1 when this path cannot take the call (no encoder in
+// the driver, a chunk size beyond what the kernel stages, a B the tensor map refuses): the caller then runs
+// the ordinary kernel.  0 = launched, negative = error.
+int launch_spmm_tma(hpspmm_ctx* ctx, int m, int nc, int64_t rows_b, const int32_t* row_ptr, const int32_t* col_idx,
+                    const float* vals, const float* B, float* C, const int32_t* chunk_start,
+                    const int32_t* chunk_row, float* carry_val, const int32_t* chunk_order, int S,
+                    int* run_counter, row_list rows, cudaStream_t stream) {
+  if (S <= 0 || S > kTmaMaxS || run_counter == nullptr || rows.nz_id == nullptr || rows_b <= 0) return 1;
+  tensor_map_encode_fn enc = tensor_map_encoder();
+  if (!enc) return 1;
+  CUtensorMap map_b;
+  const cuuint64_t gdim[2] = {128, (cuuint64_t)rows_b};
+  const cuuint64_t gstride[1] = {512};
+  const cuuint32_t box[2] = {128, 1};   // gather4: one row per box, four boxes per operation
+  const cuuint32_t estride[2] = {1, 1};
+  if (enc(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(B), gdim, gstride, box, estride,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return 1;
+  constexpr int smem = kTmaWarps * kTmaSmemPerWarp;
+  static std::once_flag once;
+  static cudaError_t attr = cudaSuccess;
+  std::call_once(once, [] {
+    attr = cudaFuncSetAttribute(spmm_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  });
+  if (attr != cudaSuccess) return 1;
+  const int n_chunk_blocks = (nc + kTmaWarps - 1) / kTmaWarps;
+  int n_zero_blocks = (m + kTmaWarps * 32 - 1) / (kTmaWarps * 32);
+  const int cap = ctx->sm_count * 4;
+  if (n_zero_blocks > cap) n_zero_blocks = cap;
+  const unsigned grid = (unsigned)(n_chunk_blocks + n_zero_blocks);
+  if (grid == 0) return 0;
+  spmm_tma_kernel<<<grid, kTmaWarps * 32, smem, stream>>>(map_b, m, nc, n_chunk_blocks, row_ptr, col_idx, vals, B, C,
+                                                          chunk_start, chunk_row, carry_val, chunk_order, S,
+                                                          run_counter, rows.nz_id, rows.nz_end, rows.chunk_ri,
+                                                          ctx->flag + HPSPMM_FLAG_TMA_FALLBACKS);
+  ctx->launches++;
+  if (cudaGetLastError() != cudaSuccess) return -1;
+  return 0;
+}
+
 }  // namespace
 
 // Nominal chunk size of the kernels that probe row_ptr or reduce into C (the allocation-free entry, the COO
@@ -1259,9 +1527,17 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
              const int32_t* row_ptr, const int32_t* col_idx, const float* vals, const float* B,
              float* C, const int32_t* chunk_start, const int32_t* chunk_row, int32_t* carry_row,
              float* carry_val, const int32_t* chunk_order, bool need_fixup, cudaStream_t stream,
-             int S = 0, int* run_counter = nullptr, row_list rows = row_list{nullptr, nullptr, nullptr}) {
+             int S = 0, int* run_counter = nullptr, row_list rows = row_list{nullptr, nullptr, nullptr},
+             int64_t tma_rows_b = 0) {
   int st;
   const int m = (int)M, nc = (int)n_chunks;
+  if (!rowsplit && K == 128 && tma_rows_b > 0) {
+    // B through the tensor memory accelerator (HPSPMM_ALGO_TMA); falls through when that path declines
+    const int r = launch_spmm_tma(ctx, m, nc, tma_rows_b, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
+                                  carry_val, chunk_order, S, run_counter, rows, stream);
+    if (r == 0) return HPSPMM_OK;
+    if (r < 0) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "spmm_tma_kernel launch", cudaGetLastError());
+  }
 #define HPSPMM_ARGS ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, stream
 #define HPSPMM_SLAB(W, STRIDED, off) \
   run_slab<W, STRIDED>(ctx, hint, m, nc, row_ptr, col_idx, vals, B + (off), C + (off), chunk_start, chunk_row, \
@@ -1466,7 +1742,8 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
     return run_spmm(ctx, hint, true, M, K, M, row_ptr, col_idx, vals, B, C, nullptr, nullptr,
                     nullptr, nullptr, nullptr, false, s);
   }
-  HPSPMM_REQUIRE(ctx, algo == HPSPMM_ALGO_AUTO || algo == HPSPMM_ALGO_BALANCED, "unknown algo");
+  HPSPMM_REQUIRE(ctx, algo == HPSPMM_ALGO_AUTO || algo == HPSPMM_ALGO_BALANCED || algo == HPSPMM_ALGO_TMA,
+                 "unknown algo");
   if (plan) {
     HPSPMM_REQUIRE(ctx, plan->M == M && plan->nnz == nnz, "plan built for another matrix");
     HPSPMM_REQUIRE(ctx, K <= plan->max_K, "K exceeds the plan's max_K");
@@ -1474,7 +1751,7 @@ int hpspmm_spmm_csr_f32(hpspmm_ctx* ctx, const hpspmm_plan* plan, int64_t M, int
     return run_spmm(ctx, hint, false, M, K, plan->n_chunks, row_ptr, col_idx, vals, B, C,
                     plan->chunk_start, plan->chunk_row, plan->carry_row, plan->carry_val,
                     plan->chunk_order, plan->n_split_chunks > 0, s, plan->chunk_nnz, plan->run_counter,
-                    row_list{plan->nz_id, plan->nz_end, plan->chunk_ri});
+                    row_list{plan->nz_id, plan->nz_end, plan->chunk_ri}, algo == HPSPMM_ALGO_TMA ? N : 0);
   }
   int32_t S = (opts && opts->chunk_nnz > 0) ? opts->chunk_nnz : hpspmm_default_chunk_nnz(K, nnz);
   S = (S + 31) / 32 * 32;

@@ -48,8 +48,13 @@ enum {
 enum {
   HPSPMM_ALGO_AUTO = 0,      /* nnz-balanced chunks, heavy rows split (the default)     */
   HPSPMM_ALGO_BALANCED = 1,  /* same as AUTO                                            */
-  HPSPMM_ALGO_ROW_SPLIT = 2  /* one sub-warp per row; the shape of the reference's
+  HPSPMM_ALGO_ROW_SPLIT = 2, /* one sub-warp per row; the shape of the reference's
                                 GESpMM kernels (spmm/mm/spmm_kernel.cu:247-370)          */
+  HPSPMM_ALGO_TMA = 3        /* BALANCED with the rows of B fetched by TMA (tile::gather4
+                                into shared memory) instead of per-lane loads.  Taken at
+                                K = 128 with a plan of nominal chunk size up to 256;
+                                any other call runs as BALANCED.  Same order of additions,
+                                hence the same bits, as BALANCED.                        */
 };
 
 /* Runtime options; zero-initialise for defaults.  Replace the reference's
@@ -509,6 +514,11 @@ HPSPMM_API int hpspmm_probe_gather_gbs(hpspmm_ctx* ctx, int32_t row_bytes, int64
                                        int64_t n_gathers, int32_t pattern, int64_t hot_rows,
                                        double hot_share, int32_t repeats, double* gbs_out,
                                        double* ms_out);
+
+/* Number of warps of the HPSPMM_ALGO_TMA kernel, since the context was created, whose bounded wait for a
+ * TMA copy ran out; such a warp finishes its chunk with ordinary loads, so results are unaffected and the
+ * count is a health check (expected: 0).  Synchronises the device. */
+HPSPMM_API int hpspmm_ctx_tma_fallbacks(hpspmm_ctx* ctx, int64_t* count);
 
 /* The same random rows through the tensor memory accelerator: producer warps fetch four rows per
  * instruction into shared memory (cp.async.bulk.tensor ... tile::gather4 on a tensor map of the table),
