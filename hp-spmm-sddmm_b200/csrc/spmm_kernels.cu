@@ -587,18 +587,28 @@ constexpr int kTmaSmemPerWarp = kTmaRing * kTmaGroupBytes + kTmaMaxChunk * 8 + k
 
 __device__ __forceinline__ uint32_t smem_addr_of(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// the slow side of a wait: polls until the phase completes or the clock limit passes
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
   const long long t0 = clock64();
   for (unsigned n = 1;; ++n) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
+    if (mbar_try(bar, parity)) return true;
     if ((n & 63u) == 0 && clock64() - t0 > kTmaSpinLimit) return false;
   }
+}
+
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity) {
+  if (mbar_try(bar, parity)) return true;   // the copy has usually landed: no clock read, no loop
+  return mbar_wait_slow(bar, parity);
 }
 
 __global__ void __launch_bounds__(kTmaWarps * 32, 3)
@@ -686,8 +696,9 @@ spmm_tma_kernel(const __grid_constant__ CUtensorMap map_b, int M, int n_chunks, 
 
   bool by_tma = true;
   int pending_from = 0;                      // first group whose copy was never seen to land
-  for (int g = 0; g < n_groups; ++g) {
-    const int b = g % kTmaRing;
+  const uint32_t bar0 = smem_addr_of(full);
+  // one group: wait for its buffer, read the four rows, hand the buffer back to the TMA, multiply
+  auto do_group = [&](int g, int b, uint32_t parity) {
     float4 rows4[4];
     float v[4];
     const int4 e01 = *reinterpret_cast<const int4*>(&ent[4 * g]);       // (col, val) x 2, broadcast
@@ -695,7 +706,7 @@ spmm_tma_kernel(const __grid_constant__ CUtensorMap map_b, int M, int n_chunks, 
     v[0] = __int_as_float(e01.y), v[1] = __int_as_float(e01.w);
     v[2] = __int_as_float(e23.y), v[3] = __int_as_float(e23.w);
     if (by_tma) {
-      const bool ok = mbar_wait_limited(smem_addr_of(&full[b]), (uint32_t)(g / kTmaRing) & 1u);
+      const bool ok = mbar_wait_limited(bar0 + 8u * (uint32_t)b, parity);
       by_tma = __all_sync(0xffffffffu, ok);
       if (!by_tma) {
         pending_from = g;
@@ -707,11 +718,11 @@ spmm_tma_kernel(const __grid_constant__ CUtensorMap map_b, int M, int n_chunks, 
 #pragma unroll
       for (int i = 0; i < 4; ++i) rows4[i] = src[i * 32];
       __syncwarp();                          // every lane has read the buffer before it is refilled
-      if ((g + 1) % kTmaBatch == 0 && issued < n_groups) {
+      if ((b + 1) % kTmaBatch == 0 && issued < n_groups) {
         // the kTmaBatch buffers of groups g - kTmaBatch + 1 .. g are free: refill them with the next groups
-        const int n_new = min(kTmaBatch, n_groups - issued);
         // (the warp's reads of these buffers are ordered before this point by the __syncwarp above; the
         // refill is ordered after it by program order, as in any mbarrier-released TMA ring)
+        const int n_new = min(kTmaBatch, n_groups - issued);
         if (lane < n_new) issue(issued + lane);
         issued += n_new;
       }
@@ -733,6 +744,15 @@ spmm_tma_kernel(const __grid_constant__ CUtensorMap map_b, int M, int n_chunks, 
           fma4(acc, v[i], rows4[i]);
         }
       }
+    }
+  };
+  // the ring is walked in whole turns so that a group's buffer index is a compile-time constant
+  for (int turn = 0; turn * kTmaRing < n_groups; ++turn) {
+    const uint32_t parity = (uint32_t)turn & 1u;
+#pragma unroll
+    for (int b = 0; b < kTmaRing; ++b) {
+      const int g = turn * kTmaRing + b;
+      if (g < n_groups) do_group(g, b, parity);
     }
   }
   if (!by_tma) {
