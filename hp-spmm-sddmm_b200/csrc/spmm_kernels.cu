@@ -1425,12 +1425,11 @@ int launch_spmm_tma(hpspmm_ctx* ctx, int m, int nc, int64_t rows_b, const int32_
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return 1;
   constexpr int smem = kTmaWarps * kTmaSmemPerWarp;
-  static std::once_flag once;
-  static cudaError_t attr = cudaSuccess;
-  std::call_once(once, [] {
-    attr = cudaFuncSetAttribute(spmm_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  });
-  if (attr != cudaSuccess) return 1;
+  // per call: the attribute belongs to the current device's context, and a process may drive several GPUs
+  if (cudaFuncSetAttribute(spmm_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return 1;
+  }
   const int n_chunk_blocks = (nc + kTmaWarps - 1) / kTmaWarps;
   int n_zero_blocks = (m + kTmaWarps * 32 - 1) / (kTmaWarps * 32);
   const int cap = ctx->sm_count * 4;
@@ -1442,7 +1441,11 @@ int launch_spmm_tma(hpspmm_ctx* ctx, int m, int nc, int64_t rows_b, const int32_
                                                           run_counter, rows.nz_id, rows.nz_end, rows.chunk_ri,
                                                           ctx->flag + HPSPMM_FLAG_TMA_FALLBACKS);
   ctx->launches++;
-  if (cudaGetLastError() != cudaSuccess) return -1;
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "spmm_tma_kernel launch", e);
+    return -1;
+  }
   return 0;
 }
 
@@ -1556,7 +1559,7 @@ int run_spmm(hpspmm_ctx* ctx, bool hint, bool rowsplit, int64_t M, int64_t K, in
     const int r = launch_spmm_tma(ctx, m, nc, tma_rows_b, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row,
                                   carry_val, chunk_order, S, run_counter, rows, stream);
     if (r == 0) return HPSPMM_OK;
-    if (r < 0) return hpspmm_set_err(ctx, HPSPMM_ERR_CUDA, "spmm_tma_kernel launch", cudaGetLastError());
+    if (r < 0) return HPSPMM_ERR_CUDA;   // the launcher has recorded the message
   }
 #define HPSPMM_ARGS ctx, hint, rowsplit, m, nc, row_ptr, col_idx, vals, B, C, chunk_start, chunk_row, carry_row, carry_val, stream
 #define HPSPMM_SLAB(W, STRIDED, off) \
