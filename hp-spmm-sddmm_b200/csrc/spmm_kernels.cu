@@ -1924,16 +1924,24 @@ static int host_products_pipelined(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_
   return HPSPMM_OK;
 }
 
-// slabs of one product: 64 columns when they divide K and leave at least two (256-byte rows copy
-// faster than 128-byte rows when both directions are busy), else 32; a width that is no multiple of 32
-// travels whole
-static int append_slabs(host_slab* out, int cap, int n, const float* B, float* C, int64_t K) {
+// Width of the column slabs a product of width K travels in.  64 columns when they divide K and leave at
+// least two slabs: with both directions busy this link moves 256-byte rows at 50 GB/s each way and 128-byte
+// rows at 36.  `others_overlap` (several products in one call): a 64-column product then travels whole, as
+// one contiguous copy, and overlaps with its neighbours instead of with itself.  Else 32; a width that is
+// no multiple of 32 travels whole.
+static int64_t host_slab_width(int64_t K, bool others_overlap) {
+  if (K % 32 != 0) return K;
+  return (K % 64 == 0 && (K >= 128 || others_overlap)) ? 64 : 32;
+}
+
+static int append_slabs(host_slab* out, int cap, int n, const float* B, float* C, int64_t K,
+                        bool others_overlap = false) {
   if (K % 32 != 0) {
     if (n >= cap) return -1;
     out[n++] = host_slab{B, C, K, K};
     return n;
   }
-  const int64_t w = (K % 64 == 0 && K >= 128) ? 64 : 32;
+  const int64_t w = host_slab_width(K, others_overlap);
   for (int64_t off = 0; off < K; off += w) {
     if (n >= cap) return -1;
     out[n++] = host_slab{B + off, C + off, K, w};
@@ -1972,7 +1980,8 @@ int hpspmm_spmm_csr_f32_host_multi(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_
   // Order of the products.  Downloads can start only after the first slab has been uploaded and multiplied, and the
   // download of the very last slab overlaps nothing, so the pipeline should begin AND end on a narrow slab: the
   // product with the narrowest slabs goes last, the next narrowest first, the others between them, widest first.
-  auto slab_width = [&](int i) { return Ks[i] % 32 != 0 ? Ks[i] : ((Ks[i] % 64 == 0 && Ks[i] >= 128) ? (int64_t)64 : (int64_t)32); };
+  const bool several = n_products >= 2;
+  auto slab_width = [&](int i) { return host_slab_width(Ks[i], several); };
   int order[16];
   for (int i = 0; i < n_products; ++i) order[i] = i;
   std::stable_sort(order, order + n_products, [&](int a, int b) {
@@ -1985,7 +1994,7 @@ int hpspmm_spmm_csr_f32_host_multi(hpspmm_ctx* ctx, int64_t M, int64_t N, int64_
     order[0] = second;
   }
   for (int i = 0; i < n_products; ++i) {
-    n = append_slabs(slabs, 16 * 16, n, Bs[order[i]], Cs[order[i]], Ks[order[i]]);
+    n = append_slabs(slabs, 16 * 16, n, Bs[order[i]], Cs[order[i]], Ks[order[i]], several);
     if (n < 0) return HPSPMM_ERR_UNSUPPORTED;
   }
   hpspmm_device_guard guard(ctx->device);
