@@ -304,6 +304,36 @@ __device__ __forceinline__ float4 reduce_groups(float4 a) {
   return a;
 }
 
+// A finished row: add the groups' partial sums and store the row.  Instead of giving every group the whole
+// sum (reduce_groups: 8 shuffles at W = 8) and letting one group store it, the groups split the work: each
+// exchange hands the partner the half it will own and keeps the other, so W = 8 takes 3 shuffles and every
+// lane stores one float (group g ends up with component g of each float4: 32 lanes, one 128-byte line),
+// W = 16 takes 2 shuffles and every lane stores a float2.  Every kept value is own + partner at each
+// step, in the same pairing as reduce_groups, so the stored bits are the same.
+template <int W>
+__device__ __forceinline__ void store_row_sum(float* __restrict__ crow, const float4& a, int g, int l) {
+  if (W == 8) {
+    const bool up2 = (g & 2) != 0, up1 = (g & 1) != 0;
+    const float s0 = up2 ? a.x : a.z, s1 = up2 ? a.y : a.w;   // the pair the partner (g ^ 2) keeps
+    float k0 = up2 ? a.z : a.x, k1 = up2 ? a.w : a.y;
+    k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+    k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+    const float s = up1 ? k0 : k1;                            // the one the partner (g ^ 1) keeps
+    float k = up1 ? k1 : k0;
+    k += __shfl_xor_sync(0xffffffffu, s, 8);
+    asm volatile("st.global.cs.f32 [%0], %1;" ::"l"(crow + l * 4 + g), "f"(k) : "memory");
+  } else if (W == 16) {
+    const bool up = (g & 1) != 0;
+    const float s0 = up ? a.x : a.z, s1 = up ? a.y : a.w;
+    float k0 = up ? a.z : a.x, k1 = up ? a.w : a.y;
+    k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+    k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+    asm volatile("st.global.cs.v2.f32 [%0], {%1,%2};" ::"l"(crow + l * 4 + g * 2), "f"(k0), "f"(k1) : "memory");
+  } else {
+    st_stream(crow + l * 4, a);
+  }
+}
+
 // In-kernel fix-up of one split row.  A row longer than S is cut at multiples of S only, so its pieces
 // are the chunks first = row_ptr[r] / S .. last = (row_ptr[r+1] - 1) / S: all but the last hand a carry
 // on, the last stores the row.  Every piece bumps the row's counter when its own part is visible
@@ -425,8 +455,7 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   // The common case (the next row is not empty, or only a few are) stays inline; a long
   // run of empty rows falls back to a binary search.
   auto finish_row = [&](int next_entry) {
-    const float4 t = reduce_groups<W>(acc);
-    if (g == 0) st_stream(C + (int64_t)row * K + l * 4, t);
+    store_row_sum<W>(C + (int64_t)row * K, acc, g, l);
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (COMPACT) {
       ++ri;
@@ -524,11 +553,11 @@ spmm_warp_kernel(int M, int n_chunks, int n_chunk_blocks, const int* __restrict_
   }
   cp_async_wait<0>();
 
-  const float4 t = reduce_groups<W>(acc);
   const bool hands_on = row_end != n1;   // the chunk ends inside `row`
   if (!hands_on) {
-    if (g == 0) st_stream(C + (int64_t)row * K + l * 4, t);
+    store_row_sum<W>(C + (int64_t)row * K, acc, g, l);
   } else {
+    const float4 t = reduce_groups<W>(acc);
     if (g == 0) *reinterpret_cast<float4*>(carry_val + (int64_t)chunk * K + l * 4) = t;
   }
   if (!SETTLE) {
