@@ -310,7 +310,8 @@ __device__ __forceinline__ float4 reduce_groups(float4 a) {
 // lane stores one float (group g ends up with component g of each float4: 32 lanes, one 128-byte line),
 // W = 16 takes 2 shuffles and every lane stores a float2.  Every kept value is own + partner at each
 // step, in the same pairing as reduce_groups, so the stored bits are the same.
-template <int W>
+// ACCUM adds the row into C with reductions (the accumulating COO product) instead of storing it.
+template <int W, bool ACCUM = false>
 __device__ __forceinline__ void store_row_sum(float* __restrict__ crow, const float4& a, int g, int l) {
   if (W == 8) {
     const bool up2 = (g & 2) != 0, up1 = (g & 1) != 0;
@@ -321,16 +322,25 @@ __device__ __forceinline__ void store_row_sum(float* __restrict__ crow, const fl
     const float s = up1 ? k0 : k1;                            // the one the partner (g ^ 1) keeps
     float k = up1 ? k1 : k0;
     k += __shfl_xor_sync(0xffffffffu, s, 8);
-    asm volatile("st.global.cs.f32 [%0], %1;" ::"l"(crow + l * 4 + g), "f"(k) : "memory");
+    if (ACCUM)
+      asm volatile("red.global.add.f32 [%0], %1;" ::"l"(crow + l * 4 + g), "f"(k) : "memory");
+    else
+      asm volatile("st.global.cs.f32 [%0], %1;" ::"l"(crow + l * 4 + g), "f"(k) : "memory");
   } else if (W == 16) {
     const bool up = (g & 1) != 0;
     const float s0 = up ? a.x : a.z, s1 = up ? a.y : a.w;
     float k0 = up ? a.z : a.x, k1 = up ? a.w : a.y;
     k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
     k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
-    asm volatile("st.global.cs.v2.f32 [%0], {%1,%2};" ::"l"(crow + l * 4 + g * 2), "f"(k0), "f"(k1) : "memory");
+    if (ACCUM)
+      asm volatile("red.global.add.v2.f32 [%0], {%1,%2};" ::"l"(crow + l * 4 + g * 2), "f"(k0), "f"(k1) : "memory");
+    else
+      asm volatile("st.global.cs.v2.f32 [%0], {%1,%2};" ::"l"(crow + l * 4 + g * 2), "f"(k0), "f"(k1) : "memory");
   } else {
-    st_stream(crow + l * 4, a);
+    if (ACCUM)
+      red_add_v4(crow + l * 4, a);
+    else
+      st_stream(crow + l * 4, a);
   }
 }
 
@@ -1153,9 +1163,16 @@ spmm_coo_warp_kernel(int64_t nnz, int S, const int* __restrict__ row_idx, const 
   int cur_row = -1;   // row of the run being accumulated
 
   auto flush = [&]() {
-    if (cur_row >= 0) {
-      const float4 t = reduce_groups<W>(acc);
-      if (g == 0) red_add_v4(C + (int64_t)cur_row * K + l * 4, t);
+    if (cur_row >= 0) {   // warp-uniform
+      if (W == 16) {
+        // the groups split the sum and every lane adds a float2: 0.378 -> 0.365 ms at K = 64 on the R-MAT
+        // bench graph.  At K = 32 thirty-two scalar reductions per row cost more than eight 16-byte ones
+        // save in shuffles (0.233 -> 0.236 ms), so that width keeps the full reduction.
+        store_row_sum<W, true>(C + (int64_t)cur_row * K, acc, g, l);
+      } else {
+        const float4 t = reduce_groups<W>(acc);
+        if (g == 0) red_add_v4(C + (int64_t)cur_row * K + l * 4, t);
+      }
     }
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
   };
