@@ -1512,6 +1512,10 @@ int32_t hpspmm_default_chunk_nnz(int64_t K, int64_t nnz) {
   // K = 64: 0.356 / 0.314 / 0.307 / 0.310 / 0.306; K = 128: 0.630 / 0.563 / 0.563 / 0.595 / 0.592.
   // Small matrices keep smaller chunks so that there are still several waves of them
   // (148 SMs x 40 resident warps x 4).
+  // Re-measured at K = 32 after the row-store exchange (S = 384 / 512 / 640 / 768 / 1024 / 1280 / 1536):
+  // 0.195 / 0.189 / 0.186 / 0.185 / 0.182 / 0.193 / 0.212 ms.  The default stays at 512 all the same: plans are
+  // shared with the SDDMM, which on the same graph takes 0.193 / 0.230 / 0.271 / 0.333 ms at S = 512 / 640 /
+  // 768 / 1024.  A caller that builds a plan for products only can ask for 1024 (hpspmm_opts.chunk_nnz).
   const int32_t floor_s = probing_chunk_nnz(K);
   const int32_t best = K <= 32 ? 512 : (K <= 64 ? 320 : 256);
   const int64_t want = nnz / 24000 / 32 * 32;
