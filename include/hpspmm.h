@@ -63,8 +63,8 @@ typedef struct hpspmm_opts {
   int32_t algo;        /* HPSPMM_ALGO_*                                              */
   int32_t chunk_nnz;   /* nominal nnz per chunk; 0 = chosen from K; multiple of 32   */
   int32_t b_l2_hint;   /* L2 evict-last policy on the gathers of B: 0 = auto (on for
-                          K >= 64, where it measured neutral; off below, where it cost
-                          8 %), 1 = off, 2 = on                                       */
+                          K >= 64: +6 % at 128 columns, neutral at 64; off below,
+                          where it costs a little), 1 = off, 2 = on                  */
   int32_t reserved;
 } hpspmm_opts;
 
